@@ -1,0 +1,408 @@
+#!/usr/bin/env python
+"""Benchmark of the paged KV-cache hot path (BASELINE.json configs[1]).
+
+Workload "llama3-8b-decode-kv": 32 layers, 32 q / 8 kv heads, head_dim 128,
+bf16, page size 16; 256 sequences with context lengths uniform in [512, 4096];
+physical pages dealt from a seeded random permutation of a pool of 1.25x the
+pages in use; K/V ~ 0.5*N(0,1). One step = one decode token for every sequence:
+in each of the 32 layers, append the new K/V row and run paged GQA decode
+attention (layer l's output is layer l+1's query). Synthetic data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 (launched with torch.distributed.run): the layers are split evenly over N
+pipeline stages and N microbatches of 256 sequences rotate through them (weak
+scaling: the KV bytes per GPU stay the same); activations hop between stages
+with NCCL send/recv.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = "llama3-8b-decode-kv"
+METRIC = "decode_tokens_per_s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    # shape overrides for small profiling captures; the defaults are the benchmark
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--ctx-lo", type=int, default=512)
+    ap.add_argument("--ctx-hi", type=int, default=4096)
+    ap.add_argument("--q-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def make_lengths(args, seed=0):
+    rng = np.random.default_rng(seed)
+    return rng.integers(args.ctx_lo, args.ctx_hi + 1, size=args.batch)
+
+
+def algorithmic_bytes_per_layer(kv_tokens, n_pages, args, es=2):
+    """decode attention: every live K/V element once, q in and out once, the
+    page list and the three per-request descriptor arrays once."""
+    B = args.batch
+    return (kv_tokens * 2 * args.kv_heads * args.head_dim * es + 2 * B * args.q_heads * args.head_dim * es
+            + 4 * (n_pages + 2 * (B + 1)))
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with NVML while the timed
+    region runs (read-only queries)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible:
+                index = int(visible.split(",")[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU oracle arm (cpu_baseline of our line, and the whole --impl reference run)
+# ---------------------------------------------------------------------------
+def cpu_reference_arm(args, steps, warmup, n_seq=32):
+    """The reference's torch path restated on the host (oracle/): one layer of
+    the workload on the first n_seq sequences per sample — append one token by
+    index assignment, gather K/V through the page table, dense fp32 attention.
+    tok/s is scaled to the full step: n_seq tokens per (sample time * layers)."""
+    from oracle import kv_math
+
+    torch.set_num_threads(os.cpu_count())
+    lens = make_lengths(args)[:n_seq] + 1
+    ps, hkv, d, hq = args.page_size, args.kv_heads, args.head_dim, args.q_heads
+    n_pages = (lens + ps - 1) // ps
+    total = int(n_pages.sum())
+    perm = np.random.default_rng(1).permutation(int(total * 1.25) + 1)[:total].astype(np.int32)
+    desc = {"indptr": np.arange(n_seq + 1, dtype=np.int32), "kv_page_indices": perm,
+            "kv_page_indptr": np.concatenate([[0], np.cumsum(n_pages)]).astype(np.int32),
+            "kv_last_page_lens": ((lens - 1) % ps + 1).astype(np.int32)}
+    g = torch.Generator().manual_seed(2)
+    pages = (torch.randn(int(total * 1.25) + 1, 2, ps, hkv, d, generator=g) * 0.5).to(torch.bfloat16)
+    q = torch.randn(n_seq, hq, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(n_seq, hkv, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(n_seq, hkv, d, generator=g).to(torch.bfloat16)
+
+    def sample():
+        kv_math.append_paged(pages, k, v, desc, ps)
+        return kv_math.paged_attention(q, pages, desc, ps, causal=False)
+
+    for _ in range(warmup):
+        sample()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        sample()
+    dt = (time.perf_counter() - t0) / steps
+    tok_s = n_seq / (dt * args.layers)
+    info = {"value": tok_s, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 of {args.layers} layers x first {n_seq} of {args.batch} sequences per step "
+                      f"({dt * 1e3:.1f} ms/sample, CPU torch, scaled to the full step)"}
+    return info, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    info, dt = cpu_reference_arm(args, max(1, args.steps), max(1, args.warmup))
+    line = {"impl": "reference", "metric": METRIC, "value": info["value"], "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config_dict(args, args.gpus), "cpu_baseline": info,
+            "e2e": {"value": info["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, n):
+    return {"workload": WORKLOAD, "layers": args.layers, "q_heads": args.q_heads, "kv_heads": args.kv_heads,
+            "head_dim": args.head_dim, "page_size": args.page_size, "sequences_per_microbatch": args.batch,
+            "microbatches": n, "context": f"U[{args.ctx_lo},{args.ctx_hi}]", "pool": "1.25x pages, seeded permutation",
+            "parallelism": f"pp{n}" if n > 1 else "single", "l2": "inputs larger than L2 (KV read per step >> 126 MB)"}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def build_microbatch(dk, pool, pta, lens, page_ids, tag):
+    """Tasks + caches of one microbatch whose pages are the given (permuted) ids."""
+    tasks, caches = [], []
+    at = 0
+    ps = pool.page_size
+    for i, n in enumerate(lens):
+        n_pg = (int(n) + ps - 1) // ps
+        t = dk.TaskData.empty(f"{tag}-{i}", int(n))
+        t.start_pos, t.seqlen = int(n), 1
+        kv = dk.PagedKVCache.empty(pta, pool)
+        kv.page_table.extend(page_ids[at : at + n_pg])
+        at += n_pg
+        tasks.append(t)
+        caches.append(kv)
+    return tasks, caches
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import deserve_b200 as dk
+    from deserve_b200 import _lib
+    from deserve_b200.engine import KVStage, RingPipeline, prepare_decode_step
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.layers % world:
+        raise SystemExit("--layers must be divisible by --gpus")
+    L = args.layers // world
+    M = world  # microbatches
+    B, ps, hq, hkv, d = args.batch, args.page_size, args.q_heads, args.kv_heads, args.head_dim
+    K, Wm = args.steps, args.warmup
+    total_steps = Wm + K
+    sm_count = _lib.device_info()[0]
+
+    # ---- pool: M microbatches, pages from a seeded permutation ---------------------
+    lens0 = make_lengths(args)
+    final_pages = int(((lens0 + 2 * total_steps + 2 + ps - 1) // ps).sum())  # room for value + e2e passes
+    pool_pages = int(np.ceil(1.25 * final_pages * M)) + 64
+    pool = dk.GpuPagePool(L, pool_pages, ps, dev, torch.bfloat16, n_kv_heads=hkv, head_dim=d)
+    perm = np.random.default_rng(1).permutation(pool_pages).astype(np.int32)
+    pta = dk.PageTableAllocator(B * M, 8192, ps, dev)
+    gen = torch.Generator(device=dev).manual_seed(2 + rank)
+    for layer in range(L):  # K/V ~ 0.5 * N(0,1)
+        pool.pages[layer].normal_(0.0, 0.5, generator=gen)
+    mbs = []
+    at = 0
+    for m in range(M):
+        n_now = int(((lens0 + ps - 1) // ps).sum())
+        tasks, caches = build_microbatch(dk, pool, pta, lens0, perm[at : at + n_now], f"mb{m}")
+        at += n_now
+        mbs.append((tasks, caches))
+    used = perm[:at]
+    pool._bitmap[used] = False
+    pool.num_avails -= len(used)
+
+    k_new = (torch.randn(M, L, B, hkv, d, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+    v_new = (torch.randn(M, L, B, hkv, d, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+    q0 = [torch.randn(B, hq, d, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + m)).to(torch.bfloat16)
+          for m in range(M)]
+    stage = KVStage(pool, hq, 0, L)
+
+    # ---- descriptors + plans of every (microbatch, token step), device resident ------
+    descs = {}
+    for s in range(total_steps):
+        for m, (tasks, caches) in enumerate(mbs):
+            descs[(m, s)] = prepare_decode_step(tasks, caches, hq, sm_count)
+            for t in tasks:
+                t.step()
+    torch.cuda.synchronize()
+
+    attn_events = []
+    launches = [0]
+
+    def stage_fn(u, m, s, x):
+        launches[0] += L * (2 + (1 if descs[(m, s)].workspace_bytes > 0 else 0))
+        return stage.forward(x, k_new[m], v_new[m], descs[(m, s)])
+
+    pipe = RingPipeline(rank, world, stage_fn, lambda m: q0[m], total_steps, dist=dist)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    # ---- warm-up (also fills the ring), then the timed K steps -----------------------
+    pipe.advance(Wm * M)
+    torch.cuda.synchronize()
+    barrier()
+    launches[0] = 0
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        torch.cuda.synchronize()
+        t_start.record()
+        pipe.advance(K * M)
+        t_end.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms = t_start.elapsed_time(t_end)
+    if world > 1:
+        tmax = torch.tensor([ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms = float(tmax.item())
+        pipe.advance(world - 1)  # drain so that every rank leaves with matching send/recv counts
+    tokens = K * M * B
+    value = tokens / (ms * 1e-3)
+    timed_launches = launches[0]
+
+    result = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": Wm,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": config_dict(args, world), "gpu_launches": timed_launches,
+        "clocks": clocks.summary(),
+    }
+
+    # ---- roofline of the dominant kernel: every attention launch bracketed by events --
+    if rank == 0:
+        m, s = 0, total_steps - 1
+        sd = descs[(m, s)]
+        x = q0[0]
+        evs = []
+
+        def on_attention(i):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            evs.append(e)
+
+        for _ in range(2):
+            evs.clear()
+            stage.forward(x, k_new[m], v_new[m], sd, on_attention)
+        torch.cuda.synchronize()
+        per_launch_ms = float(np.mean([evs[2 * i].elapsed_time(evs[2 * i + 1]) for i in range(L)]))
+        n_pages = int(sd.kv_page_indices.numel())
+        alg = algorithmic_bytes_per_layer(sd.kv_tokens, n_pages, args)
+        peak, peak_src = 6520.5, "MEASURED_PEAKS.json hbm_gbs (burst copy)"
+        try:
+            peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]
+        except Exception:
+            peak, peak_src = 6650.0, "fallback"
+        achieved = alg / (per_launch_ms * 1e-3) / 1e9
+        result["roofline"] = {"bound": "hbm", "kernel": "decode_kernel+merge_kernel (dsv_paged_decode)",
+                              "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                              "frac_of_8000": achieved / 8000.0, "traffic": None, "peak_source": peak_src,
+                              "algorithmic_bytes_per_launch": alg, "ms_per_launch": per_launch_ms}
+
+    # ---- end to end through the public API with host buffers (N = 1) -------------------
+    if world == 1 and not args.no_e2e:
+        tasks, caches = mbs[0]
+        e2e_steps = K
+        hk = torch.randn(L, B, hkv, d).mul_(0.5).to(torch.bfloat16).pin_memory()
+        hv = torch.randn(L, B, hkv, d).mul_(0.5).to(torch.bfloat16).pin_memory()
+        hq_host = torch.randn(B, hq, d).to(torch.bfloat16).pin_memory()
+        hout = torch.empty(B, hq, d, dtype=torch.bfloat16).pin_memory()
+        ws = torch.empty(128 << 20, dtype=torch.uint8, device=dev)
+        wrapper = dk.BatchDecodeWithPagedKVCacheWrapper(ws)
+
+        desc_bytes = [0]
+
+        def e2e_step():
+            dk_k = hk.to(dev, non_blocking=True)
+            dk_v = hv.to(dev, non_blocking=True)
+            x = hq_host.to(dev, non_blocking=True)
+            ctx = dk.FlashDecodeCtx.init_paged_decode_ctx(tasks, caches, wrapper)
+            wrapper.begin_forward(ctx.kv_page_indptr, ctx.kv_page_indices, ctx.kv_last_page_lens, hq, hkv, d, ps,
+                                  data_type=torch.bfloat16, indptr_host=ctx.host["kv_page_indptr"])
+            for layer in range(L):
+                pages = pool.get_layered_pages(layer)
+                dk.append_paged_kv_cache(dk_k[layer], dk_v[layer], ctx.indptr, pages, ctx.kv_page_indices,
+                                         ctx.kv_page_indptr, ctx.kv_last_page_lens)
+                x = wrapper.forward(x, pages)
+            wrapper.end_forward()
+            desc_bytes[0] = 4 * (sum(len(a) for a in ctx.host.values()) + int(wrapper._plan_host[6]) + 2 * B)
+            hout.copy_(x, non_blocking=True)
+            for t in tasks:
+                t.step()
+
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        e_ms = e0.elapsed_time(e1)
+        result["e2e"] = {"value": e2e_steps * B / (e_ms * 1e-3), "unit": "tok/s",
+                         "h2d_bytes_per_step": int(hk.numel() * 2 * 2 + hq_host.numel() * 2 + desc_bytes[0]),
+                         "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": e_ms / e2e_steps,
+                         "api": "FlashDecodeCtx.init_paged_decode_ctx + BatchDecodeWithPagedKVCacheWrapper + "
+                                "append_paged_kv_cache, pinned host K/V/q in, pinned host out"}
+    status = _lib.read_device_status()
+    if status != 0:
+        raise SystemExit(f"device self-check fired: status {status}")
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            result["cpu_baseline"], _ = cpu_reference_arm(args, 3, 1)
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -1,0 +1,16 @@
+"""deserve_b200 — the paged KV-cache hot path of DeServe for NVIDIA B200.
+
+Host classes keep the reference's names (deserve_worker/kvcache/**,
+deserve_worker/model/context/flash.py, deserve_worker/task.py); the data
+movement and attention run in hand-written sm_100a CUDA kernels behind the C
+ABI of libdeserve_kv.so (include/deserve_kv.h).
+"""
+from .context import FlashDecodeCtx, FlashForwardCtx, FlashPrefillCtx, ForwardCtx, PagedForwardCtx
+from .kvcache import (ChunkHandle, ChunkPool, CopiedPinnedMemory, CpuChunkPool, CpuPagePool, GpuPagePool,
+                      KVCacheManager, PagedKVCache, PagePool, PageTableAllocator, PageTableHandle, PinnedMemory,
+                      VirtualPagedKVCache, VirtualPagePool)
+from .ops import (BatchDecodeWithPagedKVCacheWrapper, append_paged_kv_cache, apply_rope, apply_rope_inplace,
+                  paged_decode)
+from .task import SamplingParams, TaskData, TaskManager
+
+__all__ = [n for n in dir() if not n.startswith("_")]

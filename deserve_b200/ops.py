@@ -1,0 +1,192 @@
+"""Operator entry points of the paged KV path, with the call shapes the
+reference uses at its flashinfer boundary (deserve_worker/model/layer/
+attention.py:166-192, deserve_worker/execution/exec.py:20-22, 184-198,
+227-242), implemented by libdeserve_kv.so through ctypes.
+
+All tensors must live on a CUDA device; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_PLAN_HEADER = 8
+
+
+def _i32_dev(t: torch.Tensor, name: str) -> torch.Tensor:
+    _lib.require_cuda(t)
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+def _row_stride(t: torch.Tensor, heads: int, dim: int, name: str) -> int:
+    """Token stride (elements) of a [nnz, heads, dim] tensor whose heads and dims
+    are dense (a plain tensor or a column slice of a fused projection output)."""
+    if t.dim() != 3 or t.shape[1] != heads or t.shape[2] != dim:
+        raise ValueError(f"{name} must have shape [nnz, {heads}, {dim}], got {tuple(t.shape)}")
+    if t.shape[0] > 0 and (t.stride(2) != 1 or t.stride(1) != dim):
+        raise ValueError(f"{name}: heads and head_dim must be contiguous")
+    return t.stride(0) if t.shape[0] > 1 else heads * dim
+
+
+def _pages_view(paged_kv_cache: torch.Tensor):
+    """[P, 2, page_size, n_kv_heads, head_dim] view of one layer."""
+    p = paged_kv_cache
+    if p.dim() != 5 or p.shape[1] != 2:
+        raise ValueError(f"paged_kv_cache must be [P, 2, page_size, n_kv_heads, head_dim], got {tuple(p.shape)}")
+    _, _, ps, hkv, d = p.shape
+    if p.stride(4) != 1 or p.stride(3) != d or p.stride(2) != hkv * d or p.stride(1) != ps * hkv * d:
+        raise ValueError("paged_kv_cache: a page must be contiguous")
+    return ps, hkv, d, p.stride(0)
+
+
+def append_paged_kv_cache(append_key: torch.Tensor, append_value: torch.Tensor, append_indptr: torch.Tensor,
+                          paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor, kv_indptr: torch.Tensor,
+                          kv_last_page_len: torch.Tensor) -> None:
+    """Scatter the step's new K/V rows into the last n_i token slots of each
+    request's page list (the descriptors already include the new tokens)."""
+    _lib.require_cuda(append_key, append_value, paged_kv_cache)
+    ps, hkv, d, page_stride = _pages_view(paged_kv_cache)
+    if append_key.dtype != paged_kv_cache.dtype or append_value.dtype != paged_kv_cache.dtype:
+        raise ValueError("append: K/V dtype differs from the page dtype")
+    ks = _row_stride(append_key, hkv, d, "append_key")
+    vs = _row_stride(append_value, hkv, d, "append_value")
+    nnz, batch = append_key.shape[0], kv_last_page_len.shape[0]
+    _lib.check(_lib.lib.dsv_append_paged_kv(
+        append_key.data_ptr(), append_value.data_ptr(), ks, vs, _i32_dev(append_indptr, "append_indptr").data_ptr(),
+        paged_kv_cache.data_ptr(), page_stride, _i32_dev(kv_indices, "kv_indices").data_ptr(),
+        _i32_dev(kv_indptr, "kv_indptr").data_ptr(), _i32_dev(kv_last_page_len, "kv_last_page_len").data_ptr(),
+        batch, nnz, hkv, d, ps, _lib.dtype_code(paged_kv_cache.dtype), _lib.current_stream_ptr(append_key.device)))
+
+
+def apply_rope_inplace(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, offsets: torch.Tensor,
+                       interleave: bool = True, rope_theta: float = 500000.0) -> None:
+    _lib.require_cuda(q, k)
+    if not interleave:
+        raise ValueError("only the interleaved (adjacent-pair) rotary layout of the reference is implemented")
+    if q.dtype != k.dtype:
+        raise ValueError("rope: q and k dtypes differ")
+    hq, d = q.shape[1], q.shape[2]
+    hkv = k.shape[1]
+    qs, ks = _row_stride(q, hq, d, "q"), _row_stride(k, hkv, d, "k")
+    _lib.check(_lib.lib.dsv_apply_rope_inplace(
+        q.data_ptr(), k.data_ptr(), qs, ks, _i32_dev(indptr, "indptr").data_ptr(),
+        _i32_dev(offsets, "offsets").data_ptr(), offsets.shape[0], q.shape[0], hq, hkv, d, float(rope_theta),
+        _lib.dtype_code(q.dtype), _lib.current_stream_ptr(q.device)))
+
+
+def apply_rope(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, offsets: torch.Tensor,
+               interleave: bool = True, rope_theta: float = 500000.0):
+    """Rotated copies of ragged q and k; token j of request i sits at position
+    offsets[i] + j."""
+    q2, k2 = q.clone(), k.clone()
+    apply_rope_inplace(q2, k2, indptr, offsets, interleave, rope_theta)
+    return q2, k2
+
+
+def plan_capacity(batch: int, sm_count: int = 148) -> int:
+    """int32 entries that a decode plan for `batch` requests can need."""
+    items = max(4 * sm_count, batch) + batch
+    return _PLAN_HEADER + 4 * items + 2 * batch
+
+
+def make_decode_plan(kv_indptr_host: np.ndarray, n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
+                     dtype: torch.dtype, sm_count: int, plan_out: np.ndarray) -> tuple[int, int]:
+    """Fill plan_out (int32) with the split-KV schedule; returns (int32 entries
+    used, device workspace bytes needed)."""
+    kv_indptr_host = np.ascontiguousarray(kv_indptr_host, dtype=np.int32)
+    used, ws = ctypes.c_int64(), ctypes.c_int64()
+    _lib.check(_lib.lib.dsv_decode_plan(
+        kv_indptr_host.ctypes.data, len(kv_indptr_host) - 1, n_q_heads, n_kv_heads, head_dim, page_size,
+        _lib.dtype_code(dtype), sm_count, plan_out.ctypes.data, plan_out.size, ctypes.byref(used), ctypes.byref(ws)))
+    return used.value, ws.value
+
+
+def paged_decode(q: torch.Tensor, paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor, kv_indptr: torch.Tensor,
+                 kv_last_page_len: torch.Tensor, plan_host: np.ndarray, plan_dev: torch.Tensor,
+                 workspace: torch.Tensor | None, out: torch.Tensor | None = None, sm_scale: float | None = None,
+                 lse: torch.Tensor | None = None) -> torch.Tensor:
+    """Functional form of the decode attention call: every buffer explicit."""
+    _lib.require_cuda(q, paged_kv_cache, plan_dev)
+    ps, hkv, d, page_stride = _pages_view(paged_kv_cache)
+    if q.dtype != paged_kv_cache.dtype:
+        raise ValueError("decode: q dtype differs from the page dtype")
+    batch, hq = q.shape[0], q.shape[1]
+    qs = _row_stride(q, hq, d, "q")
+    if out is None:
+        out = torch.empty((batch, hq, d), dtype=q.dtype, device=q.device)
+    os_ = _row_stride(out, hq, d, "out")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    _lib.check(_lib.lib.dsv_paged_decode(
+        q.data_ptr(), qs, paged_kv_cache.data_ptr(), page_stride, kv_indices.data_ptr(), kv_indptr.data_ptr(),
+        kv_last_page_len.data_ptr(), out.data_ptr(), os_, _lib.ptr(lse), plan_host.ctypes.data, plan_dev.data_ptr(),
+        _lib.ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(), batch, hq, hkv,
+        d, ps, _lib.dtype_code(q.dtype), float(sm_scale), _lib.current_stream_ptr(q.device)))
+    return out
+
+
+class BatchDecodeWithPagedKVCacheWrapper:
+    """begin_forward / forward / end_forward object of the reference's decode
+    path (exec.py:21, 184-198; attention.py:185). `workspace_buffer` is a uint8
+    device tensor owned by the caller: its head holds the device copy of the
+    plan, the rest the split-KV partial states."""
+
+    _PLAN_BYTES = 1 << 20
+
+    def __init__(self, workspace_buffer: torch.Tensor, kv_layout: str = "NHD"):
+        _lib.require_cuda(workspace_buffer)
+        if kv_layout != "NHD":
+            raise ValueError("only the NHD page layout of the reference is implemented")
+        if workspace_buffer.dtype != torch.uint8 or workspace_buffer.numel() < 2 * self._PLAN_BYTES:
+            raise ValueError("workspace_buffer must be a uint8 tensor of at least 2 MiB")
+        self._ws = workspace_buffer
+        self._sm_count = _lib.device_info()[0]
+        self._plan_host: np.ndarray | None = None
+        self._plan_pinned: torch.Tensor | None = None
+        self._desc = None
+
+    def begin_forward(self, indptr: torch.Tensor, indices: torch.Tensor, last_page_len: torch.Tensor,
+                      num_qo_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                      pos_encoding_mode: str = "NONE", data_type=torch.float16, *,
+                      indptr_host: np.ndarray | None = None) -> None:
+        """Plan the split-KV schedule for this batch. `indptr_host` (the same
+        values as `indptr`, in host memory) avoids a device->host copy."""
+        if pos_encoding_mode != "NONE":
+            raise ValueError("positional encoding inside attention is not part of this path")
+        if indptr_host is None:
+            indptr_host = indptr.cpu().numpy()
+        batch = len(indptr_host) - 1
+        cap = plan_capacity(batch, self._sm_count)
+        if cap * 4 > self._PLAN_BYTES:
+            raise _lib.DeserveKVError(f"decode plan for {batch} requests does not fit the workspace head")
+        pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        plan = pinned.numpy()
+        used, ws_bytes = make_decode_plan(indptr_host, num_qo_heads, num_kv_heads, head_dim, page_size,
+                                          data_type if isinstance(data_type, torch.dtype) else torch.float16,
+                                          self._sm_count, plan)
+        if ws_bytes > self._ws.numel() - self._PLAN_BYTES:
+            raise _lib.DeserveKVError(f"workspace_buffer too small: split-KV partials need {ws_bytes} bytes")
+        self._ws[: used * 4].view(torch.int32).copy_(pinned[:used], non_blocking=True)
+        self._plan_pinned, self._plan_host = pinned, plan
+        self._desc = (indptr, indices, last_page_len, num_qo_heads, num_kv_heads, head_dim, page_size)
+
+    def forward(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, sm_scale: float | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        if self._desc is None:
+            raise RuntimeError("forward() called outside begin_forward()/end_forward()")
+        indptr, indices, last_page_len, hq, hkv, d, ps = self._desc
+        if q.dim() == 2:
+            q = q.view(-1, hq, d)
+        return paged_decode(q, paged_kv_cache, indices, indptr, last_page_len, self._plan_host,
+                            self._ws[: self._PLAN_BYTES].view(torch.int32), self._ws[self._PLAN_BYTES :], out,
+                            sm_scale)
+
+    def end_forward(self) -> None:
+        self._desc = None

@@ -1,0 +1,209 @@
+/*
+ * deserve_kv.h — C ABI of libdeserve_kv.so: the paged KV-cache hot path of
+ * DeServe (CoLearn-Dev/deserve) as hand-written sm_100a CUDA kernels.
+ *
+ * Every entry point
+ *   - takes plain pointers, sizes and a CUDA stream passed as void* (a
+ *     cudaStream_t; NULL = the legacy default stream),
+ *   - validates its arguments BEFORE launching anything,
+ *   - returns 0 on success or a negative DSV_E_* code (never throws, never
+ *     exits); dsv_last_error() gives the message of the calling thread's
+ *     last failure,
+ *   - is stream-ordered and does not synchronise unless its comment says so,
+ *   - allocates nothing: all buffers belong to the caller.
+ *
+ * Page tensor layout (kept from the reference, deserve_worker/kvcache/paged/
+ * page_pool.py:25-29): pages[L, P, 2, page_size, n_kv_heads, head_dim], index
+ * 2 = {0: K, 1: V}. Kernels receive one layer's slab, pages[layer]
+ * (page_pool.py:81-82), plus the page stride in ELEMENTS
+ * (= 2 * page_size * n_kv_heads * head_dim for a contiguous pool).
+ *
+ * Ragged-batch descriptors (deserve_worker/model/context/flash.py:24-70), all
+ * int32 on the device:
+ *   qo_indptr[B+1]        prefix sum of new tokens per request
+ *   kv_indices[sum pages] page ids of every request, concatenated
+ *   kv_indptr[B+1]        prefix sum of pages per request
+ *   kv_last_page_len[B]   valid tokens in each request's last page (1..page_size)
+ * and they describe the cache AFTER the step's new tokens were appended.
+ */
+#ifndef DESERVE_KV_H_
+#define DESERVE_KV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSV_VERSION 100
+
+/* element types of K/V pages, q and out */
+#define DSV_F32 0
+#define DSV_F16 1
+#define DSV_BF16 2
+
+/* error codes */
+#define DSV_OK 0
+#define DSV_E_INVALID (-1)     /* bad argument (null pointer, size, alignment, unsupported shape) */
+#define DSV_E_CUDA (-2)        /* a CUDA runtime call failed; message holds cudaGetErrorString */
+#define DSV_E_WORKSPACE (-3)   /* caller's workspace / plan buffer too small */
+#define DSV_E_UNSUPPORTED (-4) /* valid request that this build has no kernel for */
+#define DSV_E_DEVICE (-5)      /* a kernel reported a failed bounds check or a wait that gave up */
+
+/* Library version (DSV_VERSION of the build). */
+int dsv_version(void);
+
+/* Message of the calling thread's last error ("" if none). Never NULL. */
+const char* dsv_last_error(void);
+
+/* SM count and compute capability of the current CUDA device. Synchronous, cheap. */
+int dsv_device_info(int* sm_count, int* cc_major, int* cc_minor);
+
+/*
+ * Append-scatter of one step's new K/V rows into one layer's pages.
+ * Replaces the call flashinfer.append_paged_kv_cache(xk, xv, indptr, pages,
+ * kv_page_indices, kv_page_indptr, kv_last_page_lens) at
+ * deserve_worker/model/layer/attention.py:174-183.
+ * Request i has n_i = qo_indptr[i+1]-qo_indptr[i] new tokens and post-append
+ * length len_i = (kv_indptr[i+1]-kv_indptr[i]-1)*page_size + kv_last_page_len[i];
+ * new token j goes to position t = len_i - n_i + j, i.e. page
+ * kv_indices[kv_indptr[i] + t / page_size], slot t % page_size.
+ * k, v: [nnz, n_kv_heads, head_dim] with a token stride in elements
+ * (heads and dims contiguous). Pure data movement: bit-exact.
+ */
+int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int64_t v_stride_tok,
+                        const int32_t* qo_indptr, void* pages_layer, int64_t page_stride,
+                        const int32_t* kv_indices, const int32_t* kv_indptr,
+                        const int32_t* kv_last_page_len, int batch, int nnz, int n_kv_heads,
+                        int head_dim, int page_size, int dtype, void* stream);
+
+/*
+ * Interleaved-pair rotary embedding applied in place to ragged q and k, the
+ * position of token j of request i being offsets[i] + j. Replaces
+ * flashinfer.apply_rope(xq, xk, indptr, offsets, interleave=True,
+ * rope_theta=...) at deserve_worker/model/layer/attention.py:166-173 (torch
+ * statement of the same rotation: attention.py:45-72 with the table of
+ * deserve_worker/execution/exec.py:25-55). Angles and the rotation are
+ * computed in fp32 and rounded once to the tensor type.
+ */
+int dsv_apply_rope_inplace(void* q, void* k, int64_t q_stride_tok, int64_t k_stride_tok,
+                           const int32_t* qo_indptr, const int32_t* offsets, int batch, int nnz,
+                           int n_q_heads, int n_kv_heads, int head_dim, float rope_theta,
+                           int dtype, void* stream);
+
+/*
+ * Host-side planning of the split-KV schedule for paged decode attention.
+ * Replaces BatchDecodeWithPagedKVCacheWrapper.begin_forward(...) at
+ * deserve_worker/execution/exec.py:184-192. Pure host arithmetic: reads
+ * kv_indptr_host[batch+1] (HOST memory), writes an int32 plan into plan_host
+ * (HOST memory, plan_capacity_i32 entries available) and reports how many
+ * entries it used and how many bytes of device workspace dsv_paged_decode
+ * needs for that plan. The caller copies plan_host[0..used) to the device.
+ * sm_count: SMs to balance for (dsv_device_info); <= 0 means 148.
+ */
+int dsv_decode_plan(const int32_t* kv_indptr_host, int batch, int n_q_heads, int n_kv_heads,
+                    int head_dim, int page_size, int dtype, int sm_count, int32_t* plan_host,
+                    int64_t plan_capacity_i32, int64_t* plan_used_i32,
+                    int64_t* workspace_bytes);
+
+/*
+ * Batched paged GQA decode attention over one layer's pages:
+ *   out[i,h,:] = sum_t softmax_t(q[i,h] . K[i,t,h/G] * sm_scale) * V[i,t,h/G],
+ * t in [0, len_i), G = n_q_heads / n_kv_heads, no mask, no positional term,
+ * fp32 softmax and accumulation, output rounded once to dtype. Replaces
+ * BatchDecodeWithPagedKVCacheWrapper.forward(xq, pages) at
+ * deserve_worker/model/layer/attention.py:185 (plan/end_forward:
+ * deserve_worker/execution/exec.py:184-198).
+ * q, out: [batch, n_q_heads, head_dim], token stride in elements.
+ * plan_host / plan_dev: the same plan on the host (header is read there) and
+ * on the device. workspace: device scratch of at least the size the plan
+ * reported (may be NULL when that size is 0). lse (optional, may be NULL):
+ * [batch, n_q_heads] natural-log sum-exp of the scaled scores.
+ */
+int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_layer,
+                     int64_t page_stride, const int32_t* kv_indices, const int32_t* kv_indptr,
+                     const int32_t* kv_last_page_len, void* out, int64_t out_stride_tok,
+                     float* lse, const int32_t* plan_host, const int32_t* plan_dev,
+                     void* workspace, int64_t workspace_bytes, int batch, int n_q_heads,
+                     int n_kv_heads, int head_dim, int page_size, int dtype, float sm_scale,
+                     void* stream);
+
+/*
+ * Gather scattered pages of several tasks into one dense buffer (pack), or
+ * scatter such a buffer back into pages (unpack), for the layer window
+ * [layer_begin, layer_end). Task t owns page ids
+ * page_ids[ids_indptr[t] .. ids_indptr[t+1]) (n_t of them; ids_indptr[0] = 0).
+ * In the packed buffer the tasks follow one another, task t starting at row
+ * ids_indptr[t] * (layer_end - layer_begin), and inside a task the rows are
+ * LAYER-MAJOR: row (l - layer_begin) * n_t + p holds pages[l, id_p]
+ * (page_bytes each). That is the chunk layout of
+ * KVCacheManager.copy_gpu_to_cpu / copy_cpu_to_gpu
+ * (deserve_worker/kvcache/manager.py:38-44, 63-73). page_ids and ids_indptr
+ * (n_tasks+1 entries) are DEVICE arrays. Bit-exact.
+ */
+int dsv_pack_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
+                   const int32_t* page_ids, const int32_t* ids_indptr, int n_tasks,
+                   int64_t total_ids, int layer_begin, int layer_end, void* dst, void* stream);
+int dsv_unpack_pages(const void* src, void* pages_base, int64_t layer_stride_bytes,
+                     int64_t page_bytes, const int32_t* page_ids, const int32_t* ids_indptr,
+                     int n_tasks, int64_t total_ids, int layer_begin, int layer_end,
+                     void* stream);
+
+/*
+ * Per-task offload (swap-out) and reload (swap-in) between scattered HBM pages
+ * and per-task chunks of a pinned host pool, through a device staging buffer:
+ * pack kernel -> large cudaMemcpyAsync bursts, or bursts -> unpack kernel,
+ * one layer window at a time, double-buffered over the two halves of
+ * `staging` so that the DMA of one window overlaps the pack/unpack of the
+ * next. Kernels run on stream_kernel, DMA on stream_dma; `events` are 4
+ * cudaEvent_t of the caller (timing disabled). Replaces the advanced-index
+ * gather + blocking copy_ of deserve_worker/kvcache/manager.py:24-46 and the
+ * .to("cuda") + index_put of manager.py:48-86. Task t's chunk starts at
+ * host_pool + chunk_row_begin_host[t] * page_bytes and holds
+ * num_layers * n_t rows, layer-major. ids_indptr_host is the HOST copy of
+ * ids_indptr. Half of the staging buffer must hold one layer of all tasks
+ * (total_ids * page_bytes) or the call fails with DSV_E_WORKSPACE.
+ * Asynchronous: the caller waits on both streams (swap-out: host data valid
+ * after stream_dma; swap-in: pages valid after stream_kernel).
+ */
+int dsv_swap_out_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
+                       int num_layers, const int32_t* page_ids, const int32_t* ids_indptr,
+                       const int32_t* ids_indptr_host, const int64_t* chunk_row_begin_host,
+                       int n_tasks, void* staging, int64_t staging_bytes, void* host_pool,
+                       void* stream_kernel, void* stream_dma, void** events);
+int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_stride_bytes,
+                      int64_t page_bytes, int num_layers, const int32_t* page_ids,
+                      const int32_t* ids_indptr, const int32_t* ids_indptr_host,
+                      const int64_t* chunk_row_begin_host, int n_tasks, void* staging,
+                      int64_t staging_bytes, void* stream_kernel, void* stream_dma,
+                      void** events);
+
+/*
+ * Microbatch region swap: for every layer l, copy the slab
+ * pages_base + l*layer_stride_bytes + region_offset_bytes (region_bytes long,
+ * contiguous) to host_out + l*region_bytes, then fill the same slab from
+ * host_in + l*region_bytes. All outgoing copies run on stream_out in layer
+ * order; the incoming copy of a group of layers runs on stream_in once that
+ * group's outgoing copy has finished (`event`, a cudaEvent_t of the caller,
+ * carries the edge), so both directions of the host link are busy at once.
+ * This is the data movement VirtualPagePool.swap() states in torch
+ * (deserve_worker/kvcache/virtual.py:97-113) and that swap.swap(d, h0, h1,
+ * s0, s1, interval) (deserve_worker/kvcache/swap.cpp:9-57, called from
+ * virtual.py:79-95) is meant to perform. host_out or host_in may be NULL to
+ * skip that direction. Bit-exact. Asynchronous: wait on both streams.
+ */
+int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes,
+                    int64_t region_offset_bytes, int64_t region_bytes, void* host_out,
+                    const void* host_in, void* stream_out, void* stream_in, void* event);
+
+/*
+ * Device status word of the kernels' self-checks (page id / slot / token
+ * bounds, bounded waits). Synchronises the device. *status = 0 when nothing
+ * was recorded; otherwise a DSV_E_DEVICE detail code, cleared by the call.
+ */
+int dsv_read_device_status(int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DESERVE_KV_H_ */

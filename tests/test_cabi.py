@@ -1,0 +1,102 @@
+"""The C ABI itself: every symbol of include/deserve_kv.h is exported, argument
+validation answers with error codes before any launch, and the host-side decode
+planner covers every page exactly once. No GPU needed."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from deserve_b200 import _lib, ops
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "deserve_kv.h"
+
+
+def declared_symbols() -> list[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return re.findall(r"\b(dsv_\w+)\s*\(", text)
+
+
+def test_every_declared_symbol_is_exported():
+    names = declared_symbols()
+    assert len(names) >= 12 and len(set(names)) == len(names)
+    for n in names:
+        assert hasattr(_lib.lib, n), f"{n} is declared in deserve_kv.h but not exported"
+        assert n in _lib._SIGNATURES, f"{n} has no ctypes signature"
+    assert _lib.lib.dsv_version() == 100
+
+
+def test_invalid_arguments_return_codes_not_crashes():
+    L = _lib.lib
+    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, None, None, None, 1, 1, 8, 128, 16, 2, None) == -1
+    assert "null pointer" in _lib.last_error()
+    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, None, None, None, 1, 1, 8, 128, 16, 9, None) == -1
+    assert "dtype" in _lib.last_error()
+    # nothing to do is not an error
+    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, None, None, None, 0, 0, 8, 128, 16, 2, None) == 0
+    assert L.dsv_region_swap(None, 4, 1024, 512, 1024, None, None, None, None, None) == 0  # both directions skipped
+    buf = (ctypes.c_char * 64)()
+    assert L.dsv_region_swap(buf, 4, 1024, 512, 1024, buf, None, None, None, None) == -1
+    assert "outside a layer" in _lib.last_error()
+    assert L.dsv_pack_pages(buf, 1024, 100, buf, buf, 1, 1, 0, 1, buf, None) == -1
+    assert "multiple of 16" in _lib.last_error()
+    with pytest.raises(ValueError):
+        _lib.check(-1)
+    with pytest.raises(_lib.DeserveKVError):
+        _lib.check(-3)
+
+
+def _plan(n_pages, hq=32, hkv=8, d=128, ps=16, sms=148):
+    indptr = np.concatenate([[0], np.cumsum(n_pages)]).astype(np.int32)
+    plan = np.zeros(ops.plan_capacity(len(n_pages), sms), dtype=np.int32)
+    used, ws = ops.make_decode_plan(indptr, hq, hkv, d, ps, torch.bfloat16, sms, plan)
+    return plan[:used], ws
+
+
+@pytest.mark.parametrize("seed,batch,lo,hi", [(0, 256, 32, 256), (1, 4, 7, 19), (2, 1, 4000, 4000), (3, 700, 1, 3),
+                                              (4, 5, 0, 2)])
+def test_decode_plan_covers_every_page_once(seed, batch, lo, hi):
+    rng = np.random.default_rng(seed)
+    n_pages = rng.integers(lo, hi + 1, size=batch)
+    plan, ws = _plan(n_pages)
+    n_items, slots, chunk, b = plan[1], plan[2], plan[3], plan[4]
+    assert b == batch and plan[5] == 8 and plan[6] == 8 + 4 * n_items
+    items = plan[8 : 8 + 4 * n_items].reshape(-1, 4)
+    merge = plan[plan[6] : plan[6] + 2 * batch].reshape(-1, 2)
+    cover = [np.zeros(n, dtype=int) for n in n_pages]
+    for req, pb, pe, slot in items:
+        assert 0 <= pb <= pe <= n_pages[req] and pe - pb <= chunk
+        cover[req][pb:pe] += 1
+        if merge[req][1] > 1:
+            assert merge[req][0] <= slot < merge[req][0] + merge[req][1]
+        else:
+            assert slot == -1
+    assert all((c == 1).all() for c in cover)
+    assert np.bincount(items[:, 0], minlength=batch).tolist() == merge[:, 1].tolist()
+    used_slots = sorted(s for s in items[:, 3] if s >= 0)
+    assert used_slots == list(range(slots))
+    assert ws == slots * 32 * (128 + 2) * 4
+    sizes = items[:, 2] - items[:, 1]
+    assert (np.diff(sizes) <= 0).all()  # longest first
+
+
+def test_decode_plan_balances_the_llama8b_batch():
+    rng = np.random.default_rng(0)
+    n_pages = (rng.integers(512, 4097, size=256) + 15) // 16
+    plan, _ = _plan(n_pages)
+    assert 256 <= plan[1] <= 4 * 148 + 256
+    sizes = plan[8 : 8 + 4 * plan[1]].reshape(-1, 4)
+    sizes = sizes[:, 2] - sizes[:, 1]
+    assert sizes.max() <= plan[3] and sizes.min() >= min(n_pages.min(), plan[3] // 2)
+
+
+def test_decode_plan_rejects_bad_input():
+    with pytest.raises(ValueError):
+        _plan([3, 4], hq=30, hkv=8)
+    with pytest.raises(ValueError):
+        _plan([3, 4], d=96)
+    plan = np.zeros(4, dtype=np.int32)
+    with pytest.raises(_lib.DeserveKVError, match="plan needs"):
+        ops.make_decode_plan(np.array([0, 5], dtype=np.int32), 8, 2, 64, 16, torch.float32, 148, plan)

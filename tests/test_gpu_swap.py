@@ -1,0 +1,186 @@
+"""KV swap on the GPU against the oracle: region swap, pack / unpack, and the
+per-task offload / reload into different page ids — all bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import deserve_b200 as dk
+from deserve_b200 import _lib
+from oracle import swap_ops
+from oracle.paged_alloc import OracleVirtualPool
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _fill(pool, seed):
+    g = torch.Generator().manual_seed(seed)
+    cpu = torch.randn(pool.pages.shape, generator=g).to(pool.main_dtype)
+    pool.pages.copy_(cpu)
+    return cpu
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    assert _lib.read_device_status() == 0, "a kernel self-check fired"
+
+
+@pytest.mark.parametrize("dtype,layers", [(torch.bfloat16, 5), (torch.float16, 1), (torch.float32, 8)])
+def test_region_swap_bit_exact(dtype, layers):
+    main, swap, ps, hkv, d = 6, 4, 16, 2, 64
+    pool = dk.VirtualPagePool(layers, main, swap, ps, DEV, dtype, n_kv_heads=hkv, head_dim=d)
+    ref = _fill(pool, 1)
+    size = pool.calc_swap_size()
+    prev_mb = dk.CopiedPinnedMemory(size, swap, DEV, dtype)
+    next_mb = dk.CopiedPinnedMemory(size, swap, DEV, dtype)
+    incoming = torch.randn(size, generator=torch.Generator().manual_seed(2)).to(dtype)
+    next_mb.memory.copy_(incoming)
+    prev_mb.memory.zero_()
+    want_out = torch.zeros(size, dtype=dtype)
+    lo, hi = pool.slices[1 - pool.on]
+    swap_ops.region_swap(ref, lo, hi, want_out, incoming)
+    pool.swap2(next_mb, prev_mb)
+    pool.stream.synchronize()
+    pool.stream2.synchronize()
+    assert torch.equal(prev_mb.memory.view(torch.uint8), want_out.view(torch.uint8))
+    assert torch.equal(pool.pages.cpu().view(torch.uint8), ref.view(torch.uint8))
+
+
+def test_region_state_machine_with_data_follows_a_microbatch():
+    """Two microbatches share one pool: each one's swap-region pages leave to its
+    pinned buffer while the other computes and come back intact (rounds = 3, so
+    a microbatch alternates regions and its page ids are shifted by adjust)."""
+    L, main, swap, ps, hkv, d = 2, 4, 3, 8, 2, 64
+    rounds = 3
+    pool = dk.VirtualPagePool(L, main, swap, ps, DEV, torch.bfloat16, n_kv_heads=hkv, head_dim=d)
+    pool.pages.zero_()
+    pta = dk.PageTableAllocator(16, 1024, ps, DEV)
+    pinned = [dk.CopiedPinnedMemory(pool.calc_swap_size(), swap, DEV, torch.bfloat16) for _ in range(rounds)]
+    for p in pinned:
+        p.memory.zero_()
+    caches = [None] * rounds
+    stamp = {}
+    for step in range(4 * rounds):
+        mb = step % rounds
+        pool.stream.synchronize()
+        pool.stream2.synchronize()
+        pool.switch()
+        if caches[mb] is not None:
+            offset = pool.num_pages_swap if pool.on == 1 else -pool.num_pages_swap
+            caches[mb].adjust(offset)
+            ids = caches[mb].page_table.retrieve().tolist()
+            for j, pid in enumerate(ids):  # pages are where the table says, with this microbatch's stamp
+                assert pool.pages[:, pid].float().unique().tolist() == [stamp[(mb, j)]], (step, mb, j, pid)
+        else:
+            caches[mb] = dk.VirtualPagedKVCache.empty(pta, pool)
+            caches[mb].extend([6, 3, 2][mb] * ps)  # mb0: 4 main + 2 region pages; mb1, mb2: region pages only
+            for j, pid in enumerate(caches[mb].page_table.retrieve().tolist()):
+                stamp[(mb, j)] = float(10 * (mb + 1) + j)
+                pool.pages[:, pid] = stamp[(mb, j)]
+        pool.swap2(pinned[(mb + 1) % rounds], pinned[(mb - 1 + rounds) % rounds])
+    pool.stream.synchronize()
+    pool.stream2.synchronize()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_pack_unpack_roundtrip_bit_exact(dtype):
+    L, P, ps, hkv, d = 4, 40, 16, 2, 64
+    pool = dk.GpuPagePool(L, P, ps, DEV, dtype, n_kv_heads=hkv, head_dim=d)
+    ref = _fill(pool, 3)
+    rng = np.random.default_rng(0)
+    counts = [5, 1, 9]
+    perm = rng.permutation(P)
+    id_lists = np.split(perm[: sum(counts)], np.cumsum(counts)[:-1])
+    ids = torch.tensor(np.concatenate(id_lists), dtype=torch.int32, device=DEV)
+    indptr = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    for l0, l1 in [(0, L), (1, 3)]:
+        w = l1 - l0
+        packed = torch.zeros(sum(counts) * w, *pool.pages.shape[2:], dtype=dtype, device=DEV)
+        _lib.check(_lib.lib.dsv_pack_pages(pool.pages.data_ptr(), pool.layer_stride_bytes, pool.page_bytes,
+                                           ids.data_ptr(), indptr.data_ptr(), len(counts), sum(counts), l0, l1,
+                                           packed.data_ptr(), _lib.current_stream_ptr(DEV)))
+        want = torch.cat([swap_ops.offload_rows(ref[l0:l1], x) for x in id_lists])
+        assert torch.equal(packed.cpu().view(torch.uint8), want.view(torch.uint8))
+        # scatter into a different page assignment
+        perm2 = rng.permutation(P)
+        id_lists2 = np.split(perm2[: sum(counts)], np.cumsum(counts)[:-1])
+        ids2 = torch.tensor(np.concatenate(id_lists2), dtype=torch.int32, device=DEV)
+        before = pool.pages.cpu()
+        _lib.check(_lib.lib.dsv_unpack_pages(packed.data_ptr(), pool.pages.data_ptr(), pool.layer_stride_bytes,
+                                             pool.page_bytes, ids2.data_ptr(), indptr.data_ptr(), len(counts),
+                                             sum(counts), l0, l1, _lib.current_stream_ptr(DEV)))
+        at = 0
+        for x, n in zip(id_lists2, counts):
+            swap_ops.reload_rows(before[l0:l1], x, want[at : at + n * w])
+            at += n * w
+        assert torch.equal(pool.pages.cpu().view(torch.uint8), before.view(torch.uint8))
+        ref = before
+
+
+@pytest.mark.parametrize("staging_kib", [None, 160])
+def test_offload_reload_into_new_pages_bit_exact(staging_kib):
+    """KVCacheManager: offload several tasks to pinned chunks, free and reuse
+    their pages, reload into freshly allocated ids. The small staging size forces
+    several layer windows through the double buffer."""
+    L, main, swap, ps, hkv, d = 6, 40, 4, 16, 2, 64
+    dtype = torch.bfloat16
+    pool = dk.VirtualPagePool(L, main, swap, ps, DEV, dtype, n_kv_heads=hkv, head_dim=d)
+    ref = _fill(pool, 4)
+    o_pool = OracleVirtualPool(main, swap, ps)
+    pta = dk.PageTableAllocator(16, 4096, ps, DEV)
+    chunks = dk.CpuChunkPool(L, 6, ps, dtype, n_kv_heads=hkv, head_dim=d)
+    mgr = dk.KVCacheManager(pool, chunks, pta, staging_bytes=None if staging_kib is None else staging_kib << 10)
+    caches = []
+    for tokens in (5 * ps, 1, 9 * ps - 3):
+        c = dk.VirtualPagedKVCache.empty(pta, pool)
+        c.extend(tokens)
+        caches.append(c)
+    id_lists = [c.page_table.retrieve().numpy().copy() for c in caches]
+    handles = mgr.offload_many(caches)
+    for c in caches:
+        c.free()
+    mgr.synchronize()
+    mgr.dma_stream.synchronize()
+    rows = [swap_ops.offload_rows(ref, ids) for ids in id_lists]
+    for h, want, ids in zip(handles, rows, id_lists):
+        got = h.retrieve()[: len(ids) * L]
+        assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    # overwrite the freed pages, then reload into whatever ids the pool hands out
+    pool.pages[:, torch.as_tensor(np.concatenate(id_lists), dtype=torch.long, device=DEV)] = -7.0
+    ref = pool.pages.cpu()
+    filler = dk.VirtualPagedKVCache.empty(pta, pool)
+    filler.extend(3 * ps)
+    new_caches = mgr.reload_many(handles)
+    mgr.synchronize()
+    for h in handles:
+        h.free()
+    for c, want, old in zip(new_caches, rows, id_lists):
+        new_ids = c.page_table.retrieve().numpy()
+        assert len(new_ids) == len(old)
+        assert c.isswap[: len(new_ids)].tolist() == (new_ids >= main).tolist()
+        swap_ops.reload_rows(ref, new_ids, want)
+    assert torch.equal(pool.pages.cpu().view(torch.uint8), ref.view(torch.uint8))
+    assert chunks.available_ids[-1] == [0]  # every chunk merged back
+
+
+def test_single_task_reference_api():
+    L, ps, hkv, d = 2, 8, 8, 128
+    pool = dk.VirtualPagePool(L, 12, 2, ps, DEV, torch.float16)
+    ref = _fill(pool, 6)
+    pta = dk.PageTableAllocator(4, 1024, ps, DEV)
+    chunks = dk.CpuChunkPool(L, 4, ps, torch.float16)
+    mgr = dk.KVCacheManager(pool, chunks, pta)
+    c = dk.VirtualPagedKVCache.empty(pta, pool)
+    c.extend(3 * ps)
+    old = c.page_table.retrieve().numpy().copy()
+    h = mgr.copy_gpu_to_cpu(c, "task")
+    c.free()
+    c2 = mgr.copy_cpu_to_gpu(h, "task")
+    mgr.synchronize()
+    h.free()
+    new = c2.page_table.retrieve().numpy()
+    assert not np.array_equal(old, new)
+    got = pool.pages.cpu()
+    assert torch.equal(got[:, torch.as_tensor(new, dtype=torch.long)].view(torch.uint8),
+                       ref[:, torch.as_tensor(old, dtype=torch.long)].view(torch.uint8))

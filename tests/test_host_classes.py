@@ -1,0 +1,192 @@
+"""The product's host-side KV-cache classes (reference names and signatures)
+replayed against traces recorded from the reference's own classes. Pure host
+logic: runs without a GPU."""
+import numpy as np
+import pytest
+import torch
+
+import deserve_b200 as dk
+from helpers import bits, host_traces
+
+CPU = torch.device("cpu")
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2])
+def test_allocator_trace(idx):
+    tr = host_traces()["alloc_traces"][idx]
+    pool = dk.CpuPagePool(1, tr["num_pages"], tr["page_size"], torch.float16, n_kv_heads=1, head_dim=8)
+    pta = dk.PageTableAllocator(tr["max_req"], 4096, tr["page_size"], CPU)
+    live = {}
+    for op in tr["ops"]:
+        if op["op"] == "new":
+            live[op["id"]] = dk.PagedKVCache.empty(pta, pool)
+            assert live[op["id"]].page_table.offset == op["slot"]
+        elif op["op"] == "extend":
+            c = live[op["id"]]
+            if "error" in op:
+                with pytest.raises(ValueError):
+                    c.extend(op["tokens"])
+            else:
+                assert c.extend(op["tokens"]) is True
+                assert c.page_table.retrieve().tolist() == op["table"]
+            assert pool.num_avails == op["num_avails"]
+            assert pool.page_buffer.tolist() == op["buffer"]
+        else:
+            live.pop(op["id"]).free()
+            assert pool.num_avails == op["num_avails"]
+            assert int(pool.page_bitmap.sum()) == op["bitmap_free"]
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2])
+def test_descriptor_trace(idx):
+    tr = host_traces()["desc_traces"][idx]
+    ps = tr["page_size"]
+    pool = dk.CpuPagePool(1, tr["num_pages"], ps, torch.float16, n_kv_heads=1, head_dim=8)
+    pta = dk.PageTableAllocator(len(tr["prompts"]), 4096, ps, CPU)
+    tasks = [dk.TaskData.empty(f"t{i}", p) for i, p in enumerate(tr["prompts"])]
+    caches = [dk.PagedKVCache.empty(pta, pool) for _ in tr["prompts"]]
+    for step in tr["steps"]:
+        sel_t = [tasks[i] for i in step["tasks"]]
+        sel_c = [caches[i] for i in step["tasks"]]
+        for t, n in zip(sel_t, step["seqlens"]):
+            t.init(n)
+        ctx = dk.FlashForwardCtx.init_paged_forward_ctx(sel_t, sel_c)
+        for key, want in step["desc"].items():
+            got = getattr(ctx, key)
+            assert got.dtype == torch.int32 and got.tolist() == want, key
+        assert ctx.bsz == len(sel_t) and ctx.layer_id == 0 and ctx.page_pool is pool
+        assert [c.page_table.occupied for c in sel_c] == step["occupied"]
+        for t in sel_t:
+            t.step()
+
+
+def _check_vstate(pool, st):
+    assert pool.on == st["on"]
+    assert pool.num_avails == st["num_avails"]
+    assert (pool.page_bitmap.numpy() == bits(st["bitmap"])).all()
+    assert (pool.swap_bitmap.numpy() == bits(st["swap_bitmap"])).all()
+    assert pool.swap_count == st["swap_count"]
+    assert pool.page_buffer.tolist() == st["buffer"]
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2])
+def test_virtual_pool_trace(idx):
+    tr = host_traces()["virtual_traces"][idx]
+    pool = dk.VirtualPagePool(1, tr["main"], tr["swap"], tr["page_size"], CPU, torch.float16, n_kv_heads=1, head_dim=8)
+    pta = dk.PageTableAllocator(64, 4096, tr["page_size"], CPU)
+    rounds = tr["rounds"]
+    pinned = [dk.CopiedPinnedMemory(16, tr["swap"], CPU) for _ in range(rounds)]
+    live = {}
+    for op in tr["ops"]:
+        kind = op["op"]
+        if kind == "init":
+            _check_vstate(pool, op["state"])
+        elif kind == "switch":
+            pool.switch()
+            _check_vstate(pool, op["state"])
+        elif kind == "adjust":
+            for cid, table in op["tables"].items():
+                live[int(cid)].adjust(op["offset"])
+                assert live[int(cid)].page_table.retrieve().tolist() == table
+        elif kind == "free":
+            live.pop(op["id"]).free()
+            _check_vstate(pool, op["state"])
+        elif kind == "new":
+            live[op["id"]] = dk.VirtualPagedKVCache.empty(pta, pool)
+            assert live[op["id"]].page_table.offset == op["slot"]
+        elif kind == "extend":
+            c = live[op["id"]]
+            if "error" in op:
+                with pytest.raises(ValueError):
+                    c.extend(op["tokens"])
+            else:
+                c.extend(op["tokens"])
+                assert c.page_table.retrieve().tolist() == op["table"]
+                assert c.isswap[: c.page_table.occupied].tolist() == op["isswap"]
+            _check_vstate(pool, op["state"])
+        elif kind == "swap2":
+            mb = op["mb"]
+            to = pinned[(mb - 1 + rounds) % rounds]
+            pool._handoff(pinned[(mb + 1) % rounds], to)  # the bookkeeping half of swap2 (no device here)
+            _check_vstate(pool, op["state"])
+            assert to.count == op["to_count"]
+            assert (np.asarray(to.bitmap).astype(bool) == bits(op["to_bitmap"])).all()
+
+
+@pytest.mark.parametrize("idx", [0, 1])
+def test_chunk_pool_trace(idx):
+    tr = host_traces()["chunk_traces"][idx]
+    cp = dk.CpuChunkPool(1, tr["height"], 1, torch.float16, n_kv_heads=1, head_dim=8)
+    live = {}
+    for op in tr["ops"]:
+        if op["op"] == "alloc":
+            if "error" in op:
+                with pytest.raises(RuntimeError):
+                    cp.alloc(op["size"])
+            else:
+                h = cp.alloc(op["size"])
+                assert (h.id, h.level, h.initial_size) == (op["id"], op["level"], op["size"])
+                live[(h.id, h.level)] = h
+        else:
+            live.pop((op["id"], op["level"])).free()
+        assert cp.available_ids == op["available"]
+
+
+def test_chunk_handle_rows():
+    cp = dk.CpuChunkPool(3, 4, 2, torch.float16, n_kv_heads=1, head_dim=8)
+    a, b = cp.alloc(2), cp.alloc(1)
+    assert a.retrieve().shape == (2 * 3, 2, 2, 1, 8)
+    assert (a.id, a.level, b.id, b.level) == (2, 1, 6, 0)  # split pops the last parent, alloc the first child
+    assert (a.row_begin, b.row_begin) == (12, 18)
+    assert b.retrieve().data_ptr() == cp.chunks[18:].data_ptr()
+
+
+def test_errors_match_reference_types():
+    pool = dk.CpuPagePool(1, 4, 16, torch.float16, n_kv_heads=1, head_dim=8)
+    with pytest.raises(ValueError, match="Not enough pages"):
+        pool.alloc(5)
+    pta = dk.PageTableAllocator(1, 64, 16, CPU)
+    pta.alloc()
+    with pytest.raises(ValueError, match="No available slots"):
+        pta.alloc()
+    cp = dk.CpuChunkPool(1, 3, 1, torch.float16, n_kv_heads=1, head_dim=8)
+    cp.alloc(4)
+    with pytest.raises(RuntimeError):
+        cp.alloc(1)
+
+
+def test_page_tensor_layout_and_defaults():
+    pool = dk.CpuPagePool(2, 3, 16, torch.bfloat16)
+    assert pool.pages.shape == (2, 3, 2, 16, 8, 128)
+    assert pool.get_layered_pages(1).data_ptr() == pool.pages[1].data_ptr()
+    assert pool.page_bytes == 2 * 16 * 8 * 128 * 2
+    assert pool.calc_num_pages(17) == 2
+    v = dk.VirtualPagePool(2, 4, 2, 8, CPU, torch.float16)
+    assert v.calc_swap_size() == 2 * 2 * 2 * 8 * 8 * 128
+    assert v.slices == [(4, 6), (6, 8)] and v.num_avails == 6
+
+
+def test_task_manager_page_arithmetic():
+    tm = dk.TaskManager(100, 16)
+    t = dk.TaskData.empty("a", 100)
+    tm.add(t)
+    t.init(40)
+    assert tm.calc_extended_space(["a"]) == 3 and tm.calc_rest_space("a") == 7
+    t.step()
+    assert (t.start_pos, t.seqlen) == (40, 0)
+    t.init(60)
+    assert tm.calc_delta_space("a", 60) == 4 and t.finished_prefill()
+    t.step()
+    assert (t.start_pos, t.seqlen, t.round) == (100, 1, 2)
+    assert tm.calc_occupied_space(["a"]) == 7 and tm.calc_initial_space(["a"]) == 7
+
+
+def test_kernels_refuse_cpu_tensors():
+    """No CPU fallback: an operator handed host tensors fails loudly."""
+    pages = torch.zeros(4, 2, 16, 2, 64)
+    k = torch.zeros(1, 2, 64)
+    i32 = torch.zeros(2, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        dk.append_paged_kv_cache(k, k, i32, pages, i32, i32, i32[:1])
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        dk.apply_rope(k, k, i32, i32[:1])
