@@ -143,7 +143,7 @@ int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int6
 int dsv_apply_rope_inplace(void* q, void* k, int64_t q_stride_tok, int64_t k_stride_tok,
                            const int32_t* qo_indptr, const int32_t* offsets, int batch, int nnz,
                            int n_q_heads, int n_kv_heads, int head_dim, float rope_theta,
-                           int dtype, void* stream) {
+                           const float* inv_freq_host, int dtype, void* stream) {
   using namespace dsv;
   DSV_REQUIRE(dtype_ok(dtype), "rope: unknown dtype %d", dtype);
   DSV_REQUIRE(batch >= 0 && nnz >= 0, "rope: negative batch or nnz");
@@ -157,7 +157,9 @@ int dsv_apply_rope_inplace(void* q, void* k, int64_t q_stride_tok, int64_t k_str
   RopeTable table;
   // inv_freq[i] = theta^(-2i/D): evaluated in double, rounded once to fp32
   for (int i = 0; i < head_dim / 2; ++i)
-    table.inv_freq[i] = (float)(1.0 / pow((double)rope_theta, (double)(2 * i) / (double)head_dim));
+    table.inv_freq[i] = inv_freq_host != nullptr
+                            ? inv_freq_host[i]
+                            : (float)(1.0 / pow((double)rope_theta, (double)(2 * i) / (double)head_dim));
   const int64_t total = (int64_t)nnz * (head_dim / 2);
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);

@@ -43,10 +43,17 @@ struct DecodeParams {
   int64_t q_stride, out_stride, page_stride;  // elements
   int n_q_heads, n_kv_heads, page_size;
   int hb;                   // kv heads staged per CTA (divides 8)
+  int hb_log2, ps_log2;     // log2 of hb and page_size (tensor-core kernel: both are powers of two)
   int n_qblocks;            // G / QB
   float scale_log2;         // sm_scale * log2(e)
   int* status;
 };
+
+}  // namespace
+}  // namespace dsv
+#include "decode_mma.cuh"
+namespace dsv {
+namespace {
 
 template <typename T, int D, int QB>
 __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams p) {
@@ -370,6 +377,24 @@ cudaError_t launch_decode(const DecodeParams& p, int qb, dim3 grid, size_t smem,
   }
 }
 
+template <typename T, int D>
+cudaError_t launch_decode_mma(const DecodeParams& p, bool hi, dim3 grid, size_t smem, cudaStream_t st) {
+  auto go = [&](auto kernel) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, mma_decode::kThreads, smem, st>>>(p);
+    return cudaGetLastError();
+  };
+  return hi ? go(mma_decode::decode_mma_kernel<T, D, true>) : go(mma_decode::decode_mma_kernel<T, D, false>);
+}
+
+inline int ilog2_exact(int x) {  // log2 of a power of two, -1 otherwise
+  if (x <= 0 || (x & (x - 1)) != 0) return -1;
+  int l = 0;
+  while ((1 << l) < x) ++l;
+  return l;
+}
+
 template <typename T>
 cudaError_t launch_decode_d(const DecodeParams& p, int head_dim, int qb, dim3 grid, size_t smem, cudaStream_t st) {
   if (head_dim == 128) return launch_decode<T, 128>(p, qb, grid, smem, st);
@@ -514,18 +539,38 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
   p.part_ml = p.part_o + (int64_t)slots * n_q_heads * head_dim;
   p.q_stride = q_stride_tok; p.out_stride = out_stride_tok; p.page_stride = page_stride;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
-  p.hb = hb; p.n_qblocks = G / qb; p.scale_log2 = sm_scale * kLog2e; p.status = device_status_ptr();
+  p.hb = hb; p.hb_log2 = 0; p.ps_log2 = 0; p.n_qblocks = G / qb; p.scale_log2 = sm_scale * kLog2e; p.status = device_status_ptr();
 
-  const size_t stage_bytes = (size_t)2 * page_size * hb * head_dim * es;
-  const size_t scratch = (size_t)kWarps * qb * (head_dim + 2) * sizeof(float);
-  const size_t smem = std::max(stage_bytes * kStages, scratch);
-  const dim3 grid((unsigned)n_items, (unsigned)((n_kv_heads / hb) * (G / qb)));
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  switch (dtype) {
-    case DSV_F32: e = launch_decode_d<float>(p, head_dim, qb, grid, smem, st); break;
-    case DSV_F16: e = launch_decode_d<__half>(p, head_dim, qb, grid, smem, st); break;
-    default: e = launch_decode_d<__nv_bfloat16>(p, head_dim, qb, grid, smem, st);
+  // 16-bit K/V with a GQA group of at most 16 heads and power-of-two page size:
+  // tensor-core kernel. Everything else (fp32 above all): CUDA-core kernel.
+  int hb2 = 8;
+  while (hb2 > 1 && n_kv_heads % hb2 != 0) hb2 >>= 1;
+  const int ps_log2 = ilog2_exact(page_size);
+  if (dtype != DSV_F32 && G <= 16 && ps_log2 >= 0) {
+    p.hb = hb2; p.hb_log2 = ilog2_exact(hb2); p.ps_log2 = ps_log2;
+    const bool hi = G > 8;
+    const size_t stage = (size_t)512 * head_dim;  // 2 halves x 128 rows x head_dim x 2 bytes
+    const size_t scratch = (size_t)mma_decode::kWarps * (hi ? 16 : 8) * (head_dim + 2) * sizeof(float);
+    const size_t smem = std::max(stage * mma_decode::kStages, scratch);
+    const dim3 grid((unsigned)n_items, (unsigned)(n_kv_heads / hb2));
+    if (dtype == DSV_F16)
+      e = head_dim == 128 ? launch_decode_mma<__half, 128>(p, hi, grid, smem, st)
+                          : launch_decode_mma<__half, 64>(p, hi, grid, smem, st);
+    else
+      e = head_dim == 128 ? launch_decode_mma<__nv_bfloat16, 128>(p, hi, grid, smem, st)
+                          : launch_decode_mma<__nv_bfloat16, 64>(p, hi, grid, smem, st);
+  } else {
+    const size_t stage_bytes = (size_t)2 * page_size * hb * head_dim * es;
+    const size_t scratch = (size_t)kWarps * qb * (head_dim + 2) * sizeof(float);
+    const size_t smem = std::max(stage_bytes * kStages, scratch);
+    const dim3 grid((unsigned)n_items, (unsigned)((n_kv_heads / hb) * (G / qb)));
+    switch (dtype) {
+      case DSV_F32: e = launch_decode_d<float>(p, head_dim, qb, grid, smem, st); break;
+      case DSV_F16: e = launch_decode_d<__half>(p, head_dim, qb, grid, smem, st); break;
+      default: e = launch_decode_d<__nv_bfloat16>(p, head_dim, qb, grid, smem, st);
+    }
   }
   if (e != cudaSuccess) return fail(DSV_E_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
 

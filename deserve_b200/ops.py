@@ -65,6 +65,19 @@ def append_paged_kv_cache(append_key: torch.Tensor, append_value: torch.Tensor, 
         batch, nnz, hkv, d, ps, _lib.dtype_code(paged_kv_cache.dtype), _lib.current_stream_ptr(append_key.device)))
 
 
+_INV_FREQ: dict[tuple[int, float], torch.Tensor] = {}
+
+
+def rope_inv_freq(head_dim: int, rope_theta: float) -> torch.Tensor:
+    """theta^(-2i/D) evaluated the way the reference's table is
+    (deserve_worker/execution/exec.py:44): fp32 torch arithmetic on the host."""
+    key = (head_dim, float(rope_theta))
+    if key not in _INV_FREQ:
+        _INV_FREQ[key] = (1.0 / (float(rope_theta) ** (torch.arange(0, head_dim, 2)[: head_dim // 2].float()
+                                                      / head_dim))).contiguous()
+    return _INV_FREQ[key]
+
+
 def apply_rope_inplace(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, offsets: torch.Tensor,
                        interleave: bool = True, rope_theta: float = 500000.0) -> None:
     _lib.require_cuda(q, k)
@@ -78,7 +91,7 @@ def apply_rope_inplace(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, o
     _lib.check(_lib.lib.dsv_apply_rope_inplace(
         q.data_ptr(), k.data_ptr(), qs, ks, _i32_dev(indptr, "indptr").data_ptr(),
         _i32_dev(offsets, "offsets").data_ptr(), offsets.shape[0], q.shape[0], hq, hkv, d, float(rope_theta),
-        _lib.dtype_code(q.dtype), _lib.current_stream_ptr(q.device)))
+        rope_inv_freq(d, rope_theta).data_ptr(), _lib.dtype_code(q.dtype), _lib.current_stream_ptr(q.device)))
 
 
 def apply_rope(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, offsets: torch.Tensor,

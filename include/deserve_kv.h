@@ -84,12 +84,15 @@ int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int6
  * rope_theta=...) at deserve_worker/model/layer/attention.py:166-173 (torch
  * statement of the same rotation: attention.py:45-72 with the table of
  * deserve_worker/execution/exec.py:25-55). Angles and the rotation are
- * computed in fp32 and rounded once to the tensor type.
+ * computed in fp32 and rounded once to the tensor type. inv_freq_host
+ * (optional, HOST memory, head_dim/2 floats) overrides the frequency table
+ * theta^(-2i/head_dim), e.g. with the table torch computed, so that the angles
+ * match a torch reference bit for bit; NULL derives it from rope_theta.
  */
 int dsv_apply_rope_inplace(void* q, void* k, int64_t q_stride_tok, int64_t k_stride_tok,
                            const int32_t* qo_indptr, const int32_t* offsets, int batch, int nnz,
                            int n_q_heads, int n_kv_heads, int head_dim, float rope_theta,
-                           int dtype, void* stream);
+                           const float* inv_freq_host, int dtype, void* stream);
 
 /*
  * Host-side planning of the split-KV schedule for paged decode attention.

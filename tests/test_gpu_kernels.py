@@ -85,7 +85,8 @@ def _decode_case(seed, batch, lo, hi, hq, hkv, d, ps, dtype, scale=0.5):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("hq,hkv,d,ps", [(8, 2, 64, 16), (32, 8, 128, 16), (64, 8, 128, 16), (32, 8, 128, 8),
-                                         (8, 8, 64, 16), (4, 2, 128, 4), (16, 1, 128, 16), (32, 32, 64, 16)])
+                                         (8, 8, 64, 16), (4, 2, 128, 4), (16, 1, 128, 16), (32, 32, 64, 16),
+                                         (64, 2, 64, 16), (24, 4, 128, 32), (12, 4, 64, 16)])
 def test_decode_attention_parity(dtype, hq, hkv, d, ps):
     err, _ = _decode_case(7, 13, 1, 700, hq, hkv, d, ps, dtype)
     assert err <= TOL[dtype], f"max-abs error {err}"
