@@ -49,13 +49,13 @@ _SIGNATURES = {
     "dsv_last_error": (c_char_p, []),
     "dsv_device_info": (c_int, [POINTER(c_int)] * 3),
     "dsv_read_device_status": (c_int, [POINTER(c_int)]),
-    "dsv_append_paged_kv": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
-                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "dsv_append_paged_kv": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "dsv_apply_rope_inplace": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
                                        c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
     "dsv_decode_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, _p64,
                                 _p64]),
-    "dsv_paged_decode": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+    "dsv_paged_decode": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_float, c_void_p]),
     "dsv_pack_pages": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,

@@ -21,7 +21,7 @@ __device__ __forceinline__ int find_request(const int32_t* __restrict__ indptr, 
 __global__ void __launch_bounds__(256)
 append_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, int64_t k_stride_vec,
               int64_t v_stride_vec, const int32_t* __restrict__ qo_indptr, uint4* __restrict__ pages,
-              int64_t page_stride_vec, const int32_t* __restrict__ kv_indices,
+              int64_t page_stride_vec, int64_t num_pages, const int32_t* __restrict__ kv_indices,
               const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_last_page_len,
               int batch, int nnz, int row_vecs, int page_size, int* status) {
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -46,7 +46,7 @@ append_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, int64_t 
   }
   const int page = __ldg(kv_indices + p0 + pos / page_size);
   const int slot = pos % page_size;
-  if (page < 0) {
+  if (page < 0 || page >= num_pages) {
     record_status(status, ST_BAD_PAGE_ID);
     return;
   }
@@ -105,7 +105,7 @@ extern "C" {
 
 int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int64_t v_stride_tok,
                         const int32_t* qo_indptr, void* pages_layer, int64_t page_stride,
-                        const int32_t* kv_indices, const int32_t* kv_indptr,
+                        int64_t num_pages, const int32_t* kv_indices, const int32_t* kv_indptr,
                         const int32_t* kv_last_page_len, int batch, int nnz, int n_kv_heads,
                         int head_dim, int page_size, int dtype, void* stream) {
   using namespace dsv;
@@ -114,7 +114,7 @@ int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int6
   if (batch == 0 || nnz == 0) return DSV_OK;
   DSV_REQUIRE(k && v && qo_indptr && pages_layer && kv_indices && kv_indptr && kv_last_page_len,
               "append: null pointer argument");
-  DSV_REQUIRE(n_kv_heads > 0 && head_dim > 0 && page_size > 0, "append: non-positive shape");
+  DSV_REQUIRE(n_kv_heads > 0 && head_dim > 0 && page_size > 0 && num_pages > 0, "append: non-positive shape");
   const int es = elem_size(dtype);
   const int64_t row_bytes = (int64_t)n_kv_heads * head_dim * es;
   DSV_REQUIRE(row_bytes % 16 == 0, "append: n_kv_heads*head_dim*elem_size (%lld) not a multiple of 16",
@@ -134,7 +134,7 @@ int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int6
   const int vec_per_elem = 16 / es;
   append_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
       (const uint4*)k, (const uint4*)v, k_stride_tok / vec_per_elem, v_stride_tok / vec_per_elem,
-      qo_indptr, (uint4*)pages_layer, page_stride / vec_per_elem, kv_indices, kv_indptr,
+      qo_indptr, (uint4*)pages_layer, page_stride / vec_per_elem, num_pages, kv_indices, kv_indptr,
       kv_last_page_len, batch, nnz, row_vecs, page_size, device_status_ptr());
   DSV_CUDA(cudaGetLastError());
   return DSV_OK;

@@ -43,6 +43,7 @@ enum : int {
   ST_BAD_PAGE_ID = 1,   // page id outside [0, num_pages) when the caller gave num_pages
   ST_BAD_REQUEST = 2,   // token did not map to a request / inconsistent indptr
   ST_BAD_PLAN = 3,      // plan item outside the request's page list
+  ST_WAIT_TIMEOUT = 4,  // a bounded mbarrier wait expired
 };
 
 // ---- device helpers --------------------------------------------------------

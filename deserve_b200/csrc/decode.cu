@@ -42,6 +42,7 @@ struct DecodeParams {
   float* part_ml;           // [slots][Hq][2]
   int64_t q_stride, out_stride, page_stride;  // elements
   int n_q_heads, n_kv_heads, page_size;
+  int num_pages;            // bound of the page ids
   int hb;                   // kv heads staged per CTA (divides 8)
   int hb_log2, ps_log2;     // log2 of hb and page_size (tensor-core kernel: both are powers of two)
   int n_qblocks;            // G / QB
@@ -52,6 +53,7 @@ struct DecodeParams {
 }  // namespace
 }  // namespace dsv
 #include "decode_mma.cuh"
+#include "decode_tma.cuh"
 namespace dsv {
 namespace {
 
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
 
   auto issue = [&](int j) {  // stage page j of the item
     int page = __ldg(idx + j);
-    if (page < 0) {
+    if (page < 0 || page >= p.num_pages) {
       record_status(p.status, ST_BAD_PAGE_ID);
       page = 0;
     }
@@ -492,7 +494,7 @@ int dsv_decode_plan(const int32_t* kv_indptr_host, int batch, int n_q_heads, int
 }
 
 int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_layer,
-                     int64_t page_stride, const int32_t* kv_indices, const int32_t* kv_indptr,
+                     int64_t page_stride, int64_t num_pages, const int32_t* kv_indices, const int32_t* kv_indptr,
                      const int32_t* kv_last_page_len, void* out, int64_t out_stride_tok,
                      float* lse, const int32_t* plan_host, const int32_t* plan_dev,
                      void* workspace, int64_t workspace_bytes, int batch, int n_q_heads,
@@ -508,6 +510,7 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
               "decode: n_q_heads (%d) must be a positive multiple of n_kv_heads (%d)", n_q_heads, n_kv_heads);
   DSV_REQUIRE(head_dim == 64 || head_dim == 128, "decode: head_dim %d not in {64,128}", head_dim);
   DSV_REQUIRE(page_size > 0, "decode: page_size must be positive");
+  DSV_REQUIRE(num_pages > 0 && num_pages < (1ll << 30), "decode: num_pages (%lld) out of range", (long long)num_pages);
   DSV_REQUIRE(plan_host[0] == kPlanMagic && plan_host[4] == batch && plan_host[7] == n_q_heads,
               "decode: plan does not belong to this batch (magic %x, batch %d, heads %d)", plan_host[0],
               plan_host[4], plan_host[7]);
@@ -538,7 +541,7 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
   p.part_o = static_cast<float*>(workspace);
   p.part_ml = p.part_o + (int64_t)slots * n_q_heads * head_dim;
   p.q_stride = q_stride_tok; p.out_stride = out_stride_tok; p.page_stride = page_stride;
-  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = (int)num_pages;
   p.hb = hb; p.hb_log2 = 0; p.ps_log2 = 0; p.n_qblocks = G / qb; p.scale_log2 = sm_scale * kLog2e; p.status = device_status_ptr();
 
   cudaStream_t st = (cudaStream_t)stream;
@@ -555,7 +558,29 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
     const size_t scratch = (size_t)mma_decode::kWarps * (hi ? 16 : 8) * (head_dim + 2) * sizeof(float);
     const size_t smem = std::max(stage * mma_decode::kStages, scratch);
     const dim3 grid((unsigned)n_items, (unsigned)(n_kv_heads / hb2));
-    if (dtype == DSV_F16)
+    CUtensorMap tmap;
+    const bool use_tma = ps_log2 >= 3 && page_stride == (int64_t)2 * page_size * n_kv_heads * head_dim &&
+                         tma_decode::make_pages_tensor_map(&tmap, pages_layer, page_stride, num_pages, page_size,
+                                                           n_kv_heads, head_dim, hb2, dtype == DSV_BF16);
+    if (use_tma) {
+      const size_t tsmem = std::max(stage * tma_decode::kStages + 1024 + 64, scratch + 1024);
+      auto go = [&](auto kernel) -> cudaError_t {
+        cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem);
+        if (er != cudaSuccess) return er;
+        kernel<<<grid, tma_decode::kThreads, tsmem, st>>>(tmap, p);
+        return cudaGetLastError();
+      };
+      if (dtype == DSV_F16)
+        e = head_dim == 128 ? (hi ? go(tma_decode::decode_tma_kernel<__half, 128, true>)
+                                  : go(tma_decode::decode_tma_kernel<__half, 128, false>))
+                            : (hi ? go(tma_decode::decode_tma_kernel<__half, 64, true>)
+                                  : go(tma_decode::decode_tma_kernel<__half, 64, false>));
+      else
+        e = head_dim == 128 ? (hi ? go(tma_decode::decode_tma_kernel<__nv_bfloat16, 128, true>)
+                                  : go(tma_decode::decode_tma_kernel<__nv_bfloat16, 128, false>))
+                            : (hi ? go(tma_decode::decode_tma_kernel<__nv_bfloat16, 64, true>)
+                                  : go(tma_decode::decode_tma_kernel<__nv_bfloat16, 64, false>));
+    } else if (dtype == DSV_F16)
       e = head_dim == 128 ? launch_decode_mma<__half, 128>(p, hi, grid, smem, st)
                           : launch_decode_mma<__half, 64>(p, hi, grid, smem, st);
     else

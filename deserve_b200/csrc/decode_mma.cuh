@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
       int page = 0;
       if (valid) {
         page = __ldg(idx + (gt >> ps_log));
-        if (page < 0) {
+        if (page < 0 || page >= p.num_pages) {
           record_status(p.status, ST_BAD_PAGE_ID);
           page = 0;
         }

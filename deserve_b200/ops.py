@@ -60,7 +60,7 @@ def append_paged_kv_cache(append_key: torch.Tensor, append_value: torch.Tensor, 
     nnz, batch = append_key.shape[0], kv_last_page_len.shape[0]
     _lib.check(_lib.lib.dsv_append_paged_kv(
         append_key.data_ptr(), append_value.data_ptr(), ks, vs, _i32_dev(append_indptr, "append_indptr").data_ptr(),
-        paged_kv_cache.data_ptr(), page_stride, _i32_dev(kv_indices, "kv_indices").data_ptr(),
+        paged_kv_cache.data_ptr(), page_stride, paged_kv_cache.shape[0], _i32_dev(kv_indices, "kv_indices").data_ptr(),
         _i32_dev(kv_indptr, "kv_indptr").data_ptr(), _i32_dev(kv_last_page_len, "kv_last_page_len").data_ptr(),
         batch, nnz, hkv, d, ps, _lib.dtype_code(paged_kv_cache.dtype), _lib.current_stream_ptr(append_key.device)))
 
@@ -138,7 +138,8 @@ def paged_decode(q: torch.Tensor, paged_kv_cache: torch.Tensor, kv_indices: torc
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
     _lib.check(_lib.lib.dsv_paged_decode(
-        q.data_ptr(), qs, paged_kv_cache.data_ptr(), page_stride, kv_indices.data_ptr(), kv_indptr.data_ptr(),
+        q.data_ptr(), qs, paged_kv_cache.data_ptr(), page_stride, paged_kv_cache.shape[0], kv_indices.data_ptr(),
+        kv_indptr.data_ptr(),
         kv_last_page_len.data_ptr(), out.data_ptr(), os_, _lib.ptr(lse), plan_host.ctypes.data, plan_dev.data_ptr(),
         _lib.ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(), batch, hq, hkv,
         d, ps, _lib.dtype_code(q.dtype), float(sm_scale), _lib.current_stream_ptr(q.device)))

@@ -69,11 +69,13 @@ int dsv_device_info(int* sm_count, int* cc_major, int* cc_minor);
  * new token j goes to position t = len_i - n_i + j, i.e. page
  * kv_indices[kv_indptr[i] + t / page_size], slot t % page_size.
  * k, v: [nnz, n_kv_heads, head_dim] with a token stride in elements
- * (heads and dims contiguous). Pure data movement: bit-exact.
+ * (heads and dims contiguous). num_pages: pages in the layer slab; a page id
+ * outside [0, num_pages) is skipped and recorded in the device status word.
+ * Pure data movement: bit-exact.
  */
 int dsv_append_paged_kv(const void* k, const void* v, int64_t k_stride_tok, int64_t v_stride_tok,
                         const int32_t* qo_indptr, void* pages_layer, int64_t page_stride,
-                        const int32_t* kv_indices, const int32_t* kv_indptr,
+                        int64_t num_pages, const int32_t* kv_indices, const int32_t* kv_indptr,
                         const int32_t* kv_last_page_len, int batch, int nnz, int n_kv_heads,
                         int head_dim, int page_size, int dtype, void* stream);
 
@@ -121,10 +123,15 @@ int dsv_decode_plan(const int32_t* kv_indptr_host, int batch, int n_q_heads, int
  * plan_host / plan_dev: the same plan on the host (header is read there) and
  * on the device. workspace: device scratch of at least the size the plan
  * reported (may be NULL when that size is 0). lse (optional, may be NULL):
- * [batch, n_q_heads] natural-log sum-exp of the scaled scores.
+ * [batch, n_q_heads] natural-log sum-exp of the scaled scores. num_pages:
+ * pages in the layer slab (bound of the page ids and of the TMA tensor map).
+ * Kernel choice: 16-bit K/V, GQA group <= 16, power-of-two page size >= 8 and
+ * a dense pool (page_stride = one page) run the TMA + tensor-core kernel;
+ * other 16-bit shapes the cp.async + tensor-core kernel; fp32 (and GQA groups
+ * above 16) the CUDA-core kernel.
  */
 int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_layer,
-                     int64_t page_stride, const int32_t* kv_indices, const int32_t* kv_indptr,
+                     int64_t page_stride, int64_t num_pages, const int32_t* kv_indices, const int32_t* kv_indptr,
                      const int32_t* kv_last_page_len, void* out, int64_t out_stride_tok,
                      float* lse, const int32_t* plan_host, const int32_t* plan_dev,
                      void* workspace, int64_t workspace_bytes, int batch, int n_q_heads,

@@ -30,12 +30,12 @@ def test_every_declared_symbol_is_exported():
 
 def test_invalid_arguments_return_codes_not_crashes():
     L = _lib.lib
-    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, None, None, None, 1, 1, 8, 128, 16, 2, None) == -1
+    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, 4, None, None, None, 1, 1, 8, 128, 16, 2, None) == -1
     assert "null pointer" in _lib.last_error()
-    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, None, None, None, 1, 1, 8, 128, 16, 9, None) == -1
+    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, 4, None, None, None, 1, 1, 8, 128, 16, 9, None) == -1
     assert "dtype" in _lib.last_error()
     # nothing to do is not an error
-    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, None, None, None, 0, 0, 8, 128, 16, 2, None) == 0
+    assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, 4, None, None, None, 0, 0, 8, 128, 16, 2, None) == 0
     assert L.dsv_region_swap(None, 4, 1024, 512, 1024, None, None, None, None, None) == 0  # both directions skipped
     buf = (ctypes.c_char * 64)()
     assert L.dsv_region_swap(buf, 4, 1024, 512, 1024, buf, None, None, None, None) == -1
