@@ -17,6 +17,7 @@ from . import build as _build
 LIB_PATH = Path(__file__).resolve().parent / "libdeserve_kv.so"
 
 DSV_F32, DSV_F16, DSV_BF16 = 0, 1, 2
+STATIC_SCRATCH_BYTES = 16 << 20
 E_INVALID, E_CUDA, E_WORKSPACE, E_UNSUPPORTED, E_DEVICE = -1, -2, -3, -4, -5
 
 _DTYPES = {torch.float32: DSV_F32, torch.float16: DSV_F16, torch.bfloat16: DSV_BF16}
@@ -58,6 +59,9 @@ _SIGNATURES = {
     "dsv_paged_decode": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_float, c_void_p]),
+    "dsv_paged_decode_static": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_float, c_void_p]),
     "dsv_pack_pages": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                c_void_p]),
     "dsv_unpack_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int,

@@ -617,4 +617,54 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
   return DSV_OK;
 }
 
+// ---- decode without a caller workspace ------------------------------------------------------
+// Scratch for the split-KV partial states of dsv_paged_decode_static. In host code this
+// name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_decode_scratch[DSV_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxScratchDevices = 64;
+void* g_scratch_ptr[kMaxScratchDevices] = {nullptr};
+
+// Device address of g_decode_scratch on the current device, resolved once per device.
+int static_scratch(void** out) {
+  int dev = -1;
+  DSV_CUDA(cudaGetDevice(&dev));
+  DSV_REQUIRE(dev >= 0 && dev < kMaxScratchDevices, "decode_static: device ordinal %d not supported", dev);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    DSV_CUDA(cudaGetSymbolAddress(&ptr, g_decode_scratch));
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return DSV_OK;
+}
+}  // namespace
+
+int dsv_paged_decode_static(const void* q, int64_t q_stride_tok, const void* pages_layer,
+                            int64_t page_stride, int64_t num_pages, const int32_t* kv_indices,
+                            const int32_t* kv_indptr, const int32_t* kv_last_page_len, void* out,
+                            int64_t out_stride_tok, float* lse, const int32_t* plan_host,
+                            const int32_t* plan_dev, int batch, int n_q_heads, int n_kv_heads,
+                            int head_dim, int page_size, int dtype, float sm_scale, void* stream) {
+  using namespace dsv;
+  if (batch == 0) return DSV_OK;
+  DSV_REQUIRE(plan_host != nullptr, "decode_static: null plan");
+  DSV_REQUIRE(plan_host[0] == kPlanMagic && plan_host[2] >= 0 && n_q_heads > 0 && head_dim > 0,
+              "decode_static: not a decode plan");
+  const int64_t need = (int64_t)plan_host[2] * n_q_heads * (head_dim + 2) * (int64_t)sizeof(float);
+  if (need > (int64_t)DSV_STATIC_SCRATCH_BYTES)
+    return fail(DSV_E_WORKSPACE,
+                "decode_static: this plan's partial states need %lld bytes, the built-in scratch holds %lld; "
+                "use dsv_paged_decode with a caller workspace",
+                (long long)need, (long long)DSV_STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != DSV_OK) return rc;
+  return dsv_paged_decode(q, q_stride_tok, pages_layer, page_stride, num_pages, kv_indices, kv_indptr,
+                          kv_last_page_len, out, out_stride_tok, lse, plan_host, plan_dev, scratch,
+                          (int64_t)DSV_STATIC_SCRATCH_BYTES, batch, n_q_heads, n_kv_heads, head_dim, page_size,
+                          dtype, sm_scale, stream);
+}
+
 }  // extern "C"

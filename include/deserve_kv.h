@@ -139,6 +139,35 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
                      void* stream);
 
 /*
+ * dsv_paged_decode for callers that cannot allocate device memory. It has no
+ * counterpart in the reference. Same arguments and results as dsv_paged_decode,
+ * minus the workspace: the split-KV partial states live in a fixed scratch
+ * array inside the library (DSV_STATIC_SCRATCH_BYTES, held by every GPU that
+ * loads the library until the process exits). Meant for hosts that bind this C
+ * ABI directly and have no device allocator left to ask: a serving worker that
+ * gave all remaining HBM to the page pool at start-up, so a later cudaMalloc
+ * fails or forces the pool to shrink; or a decode loop that cannot afford the
+ * device-wide synchronisation a cudaMalloc / cudaFree implies.
+ *  - The call allocates nothing (no cudaMalloc/cudaFree, no library allocator).
+ *  - A plan whose partial states need more than DSV_STATIC_SCRATCH_BYTES is
+ *    rejected with DSV_E_WORKSPACE before anything is launched.
+ *  - The first call on each device resolves the scratch array's device address
+ *    (with that device current); make that first call before any stream
+ *    capture begins.
+ *  - All calls on a device share the one array. Nothing in it has to start at
+ *    zero (every partial state is written before it is read within a call), but
+ *    two calls that overlap on the GPU (different streams) race on it:
+ *    serialise them.
+ */
+#define DSV_STATIC_SCRATCH_BYTES (16 << 20)
+int dsv_paged_decode_static(const void* q, int64_t q_stride_tok, const void* pages_layer,
+                            int64_t page_stride, int64_t num_pages, const int32_t* kv_indices,
+                            const int32_t* kv_indptr, const int32_t* kv_last_page_len, void* out,
+                            int64_t out_stride_tok, float* lse, const int32_t* plan_host,
+                            const int32_t* plan_dev, int batch, int n_q_heads, int n_kv_heads,
+                            int head_dim, int page_size, int dtype, float sm_scale, void* stream);
+
+/*
  * Gather scattered pages of several tasks into one dense buffer (pack), or
  * scatter such a buffer back into pages (unpack), for the layer window
  * [layer_begin, layer_end). Task t owns page ids
