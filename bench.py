@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (BASELINE config 3)")
+    ap.add_argument("--swap-seqs", type=int, default=64)
+    ap.add_argument("--swap-tokens", type=int, default=2048)
     return ap.parse_args()
 
 
@@ -208,6 +211,89 @@ def build_microbatch(dk, pool, pta, lens, page_ids, tag):
     return tasks, caches
 
 
+def host_link_peak(dev, nbytes=1 << 30, reps=5):
+    """Best-of-reps pinned cudaMemcpyAsync bandwidth in each direction (GB/s)."""
+    host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    devb = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, dst, src in (("h2d", devb, host), ("d2h", host, devb)):
+        best = 0.0
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dst.copy_(src, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            best = max(best, nbytes / (a.elapsed_time(b) * 1e-3) / 1e9)
+        out[name] = best
+    return out
+
+
+def swap_stress(dk, pool, free_ids, args, dev, decode_step):
+    """BASELINE config 3: the KV of swap_seqs x swap_tokens tokens, all layers, scattered over the
+    permuted pool, is swapped out to pinned host chunks and back into DIFFERENT pages while decode
+    attention of another microbatch runs on the main stream. Bit-exactness is checked with a 32-bit
+    checksum of every (layer, page) before and after, and exactly on the first and last layer."""
+    ps, L = pool.page_size, pool.num_layers
+    n_seq, n_pg = args.swap_seqs, (args.swap_tokens + ps - 1) // ps
+    total = n_seq * n_pg
+    free_ids = free_ids[pool._bitmap[free_ids]]  # pages the decode microbatch grew into since are not free
+    ids_a = torch.from_numpy(np.ascontiguousarray(free_ids[:total]).astype(np.int64)).to(dev)
+    height = int(np.ceil(np.log2(max(total, 2)))) + 1
+    peak = host_link_peak(dev)
+    chunks = dk.CpuChunkPool(L, height, ps, pool.main_dtype, n_kv_heads=pool.n_kv_heads, head_dim=pool.head_dim)
+    pta = dk.PageTableAllocator(n_seq, n_pg * ps, ps, dev)
+    mgr = dk.KVCacheManager(pool, chunks, pta, staging_bytes=4 * total * pool.page_bytes + 1024)
+    caches = []
+    for i in range(n_seq):
+        kv = dk.VirtualPagedKVCache.empty(pta, pool)
+        kv.page_table.extend(free_ids[i * n_pg : (i + 1) * n_pg])
+        caches.append(kv)
+    pool._bitmap[free_ids[:total]] = False
+    pool.num_avails -= total
+
+    def checksums(ids):
+        return torch.stack([pool.pages[l, ids].view(torch.int32).sum(dim=(1, 2, 3, 4), dtype=torch.int64)
+                            for l in range(L)])
+
+    before = checksums(ids_a)
+    first, last = pool.pages[0, ids_a].clone(), pool.pages[L - 1, ids_a].clone()
+    nbytes = total * L * pool.page_bytes
+    decode_stream = torch.cuda.Stream(device=dev)
+    steps = 24
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        cur = torch.cuda.current_stream(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(cur)
+        res = fn()  # asynchronous: pack/unpack kernels and DMA bursts are only queued here
+        with torch.cuda.stream(decode_stream):  # meanwhile another microbatch decodes
+            for _ in range(steps):
+                decode_step()
+        cur.wait_stream(mgr.stream)
+        cur.wait_stream(mgr.dma_stream)
+        e1.record(cur)
+        torch.cuda.synchronize()
+        return res, nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+    handles, out_gbs = timed(lambda: mgr.offload_many(caches))
+    for kv in caches:
+        kv.free()
+    pool.pages[:, ids_a] = 0  # the old pages are gone
+    new_caches, in_gbs = timed(lambda: mgr.reload_many(handles))
+    ids_b = torch.from_numpy(np.concatenate([c.page_table.retrieve_np() for c in new_caches]).astype(np.int64)).to(dev)
+    moved = int((ids_a != ids_b).sum().item())
+    ok = bool(torch.equal(before, checksums(ids_b)) and torch.equal(first, pool.pages[0, ids_b])
+              and torch.equal(last, pool.pages[L - 1, ids_b]))
+    for h in handles:
+        h.free()
+    return {"bytes_each_way": nbytes, "out_GBps": out_gbs, "in_GBps": in_gbs, "host_link_peak_d2h_GBps": peak["d2h"],
+            "host_link_peak_h2d_GBps": peak["h2d"], "frac_out": out_gbs / peak["d2h"], "frac_in": in_gbs / peak["h2d"],
+            "bit_exact": ok, "pages_that_changed_id": moved, "pages": total, "layers": L,
+            "concurrent": f"{steps} decode steps of the 256-sequence microbatch on another stream"}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -237,7 +323,10 @@ def run_ours(args):
     lens0 = make_lengths(args)
     final_pages = int(((lens0 + 2 * total_steps + 2 + ps - 1) // ps).sum())  # room for value + e2e passes
     pool_pages = int(np.ceil(1.25 * final_pages * M)) + 64
-    pool = dk.GpuPagePool(L, pool_pages, ps, dev, torch.bfloat16, n_kv_heads=hkv, head_dim=d)
+    do_swap = world == 1 and not args.no_swap
+    swap_pages = args.swap_seqs * ((args.swap_tokens + ps - 1) // ps) if do_swap else 0
+    pool_pages += 2 * swap_pages  # the swapped tasks' pages, and the different pages they come back to
+    pool = dk.VirtualPagePool(L, pool_pages, 0, ps, dev, torch.bfloat16, n_kv_heads=hkv, head_dim=d)
     perm = np.random.default_rng(1).permutation(pool_pages).astype(np.int32)
     pta = dk.PageTableAllocator(B * M, 8192, ps, dev)
     gen = torch.Generator(device=dev).manual_seed(2 + rank)
@@ -393,6 +482,9 @@ def run_ours(args):
                          "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": e_ms / e2e_steps,
                          "api": "FlashDecodeCtx.init_paged_decode_ctx + BatchDecodeWithPagedKVCacheWrapper + "
                                 "append_paged_kv_cache, pinned host K/V/q in, pinned host out"}
+    if do_swap:
+        result["swap"] = swap_stress(dk, pool, perm[at:], args, dev, lambda: stage.forward(
+            q0[0], k_new[0], v_new[0], descs[(0, total_steps - 1)]))
     status = _lib.read_device_status()
     if status != 0:
         raise SystemExit(f"device self-check fired: status {status}")
