@@ -9,8 +9,8 @@ from .context import FlashDecodeCtx, FlashForwardCtx, FlashPrefillCtx, ForwardCt
 from .kvcache import (ChunkHandle, ChunkPool, CopiedPinnedMemory, CpuChunkPool, CpuPagePool, GpuPagePool,
                       KVCacheManager, PagedKVCache, PagePool, PageTableAllocator, PageTableHandle, PinnedMemory,
                       VirtualPagedKVCache, VirtualPagePool)
-from .ops import (BatchDecodeWithPagedKVCacheWrapper, append_paged_kv_cache, apply_rope, apply_rope_inplace,
-                  paged_decode)
+from .ops import (BatchDecodeWithPagedKVCacheWrapper, BatchPrefillWithPagedKVCacheWrapper, append_paged_kv_cache,
+                  apply_rope, apply_rope_inplace, paged_decode, paged_prefill)
 from .task import SamplingParams, TaskData, TaskManager
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -1,0 +1,620 @@
+// Ragged causal attention of new q rows against paged K/V (chunked prefill and
+// mixed prefill+decode batches) on the 5th-generation tensor cores.
+//
+// One CTA owns one work item: (request, kv head, tile of 128/G q tokens), G =
+// n_q_heads / n_kv_heads. The G q heads of the kv head are stacked with the
+// tokens into the 128 rows of the MMA (row = token * G + head), so a K/V tile is
+// loaded once for the whole GQA group. Per 128-token K/V tile:
+//     S = Q K^T      tcgen05.mma (kind::f16, M=128, N=128, K=16 x D/16), A and B from
+//                    128B-swizzled shared memory, accumulator in TMEM (double buffered)
+//     softmax        warps 0-3, one thread per row: tcgen05.ld of the row, causal / length
+//                    mask, running maximum with lazy rescaling (O is only rescaled when a
+//                    row maximum grew by more than 2^8), P = exp2(...) packed to 16 bit and
+//                    written back to TMEM with tcgen05.st
+//     O += P V       tcgen05.mma with A = P from TMEM and B = the V tile read MN-major
+//                    (tokens are the K dimension), accumulator O in TMEM
+// Warp 4 is the TMA producer (q tile once; K and V tiles through two 2-stage rings,
+// one cp.async.bulk.tensor per 16-token box and 64-element half of head_dim),
+// warp 5 issues the MMAs from one thread and signals completion with
+// tcgen05.commit on mbarriers. Every wait is bounded; on expiry the kernel records
+// ST_WAIT_TIMEOUT, leaves the loops, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <algorithm>
+#include <type_traits>
+#include <vector>
+
+#include "common.cuh"
+
+namespace dsv {
+namespace {
+
+constexpr int kBN = 128;                 // kv tokens per tile
+constexpr int kThreads = 192;            // 4 softmax warps, producer warp, MMA warp
+constexpr int kSpinLimit = 1 << 21;
+constexpr int32_t kPrefillMagic = 0x44535032;  // "DSP2"
+constexpr int kPlanHeader = 8;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+struct PrefillParams {
+  const int32_t* qo_indptr;
+  const int32_t* kv_indices;
+  const int32_t* kv_indptr;
+  const int32_t* kv_last_page_len;
+  void* out;
+  const int4* items;  // {request, first q token of the tile (request-relative), q tokens in the tile, visible kv length of its last token}
+  int64_t out_stride;
+  int n_q_heads, n_kv_heads, ps_log2, num_pages, causal;
+  float scale_log2;
+  int* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+  for (int i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 128) __nanosleep(64);
+  }
+  record_status(status, ST_WAIT_TIMEOUT);
+  return false;
+}
+// The same wait made warp-uniform: every lane leaves with the same answer, so the
+// warp-collective tcgen05 instructions that follow are executed by all lanes or by none.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int* status) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, status));
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::
+          "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::
+          "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::
+          "r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version field.
+// K-major: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO); LBO unused (1).
+// MN-major: 64-element blocks of the MN dimension `lbo_bytes` apart, 8-row groups of the
+// K dimension 1024 bytes apart (SBO).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: fp32 accumulate, A/B format (0 = f16, 1 = bf16),
+// B major-ness (0 = K, 1 = MN), N >> 3, M >> 4.
+__host__ __device__ constexpr uint32_t instr_desc(int ab_format, int b_mn_major, int n, int m) {
+  return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+               const PrefillParams p) {
+  constexpr int DH = D / 64;
+  constexpr int QTILE = 128 * D * 2;      // q tile bytes: [DH][128 rows][128 B]
+  constexpr int KVTILE = kBN * D * 2;     // one K (or V) stage: [DH][128 tokens][128 B]
+  constexpr int HALF_ROWS = 128 * 128;    // bytes of one 64-element half: 128 rows x 128 B
+  constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  constexpr uint32_t IDESC_QK = instr_desc(kBf16 ? 1 : 0, 0, kBN, 128);
+  constexpr uint32_t IDESC_PV = instr_desc(kBf16 ? 1 : 0, 1, D, 128);
+  // TMEM columns
+  constexpr uint32_t COL_S0 = 0, COL_S1 = 384, COL_P = 128, COL_O = 256;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = q_smem + QTILE;             // 2 stages
+  const uint32_t v_smem = k_smem + 2 * KVTILE;        // 2 stages
+  const uint32_t bars = v_smem + 2 * KVTILE;
+  // barrier slots (8 bytes each)
+  const uint32_t bar_q = bars, bar_kfull = bars + 8, bar_vfull = bars + 24, bar_kempty = bars + 40,
+                 bar_vempty = bars + 56, bar_sfull = bars + 72, bar_pfull = bars + 88, bar_odone = bars + 96;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 104);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bars - base) + 108);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int tq = 128 / G;
+  const int kv_head = blockIdx.y;
+  const int ps_log = p.ps_log2, ps = 1 << ps_log;
+  const int bt = min(ps, 16), n_boxes = kBN / bt;
+
+  const int4 item = p.items[blockIdx.x];
+  const int req = item.x, q0 = item.y, nq = item.z, kv_hi = item.w;
+  const int q_begin = __ldg(p.qo_indptr + req);
+  const int n_new = __ldg(p.qo_indptr + req + 1) - q_begin;
+  const int ip0 = __ldg(p.kv_indptr + req), ip1 = __ldg(p.kv_indptr + req + 1);
+  const int kv_len = ip1 > ip0 ? (ip1 - ip0 - 1) * ps + __ldg(p.kv_last_page_len + req) : 0;
+  const int n_tiles = (kv_hi + kBN - 1) / kBN;
+  const bool bad = q0 < 0 || nq < 1 || nq > tq || q0 + nq > n_new || kv_hi < 1 || kv_hi > kv_len;
+  if (bad) {
+    if (tid == 0) record_status(p.status, ST_BAD_PLAN);
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_kfull + 8 * s, 1);
+      mbar_init(bar_vfull + 8 * s, 1);
+      mbar_init(bar_kempty + 8 * s, 1);
+      mbar_init(bar_vempty + 8 * s, 1);
+      mbar_init(bar_sfull + 8 * s, 1);
+    }
+    mbar_init(bar_pfull, 128);
+    mbar_init(bar_odone, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 4) {  // TMEM: all 512 columns (one CTA per SM)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ================================ TMA producer =============================================
+    if (lane == 0) {
+      mbar_expect_tx(bar_q, QTILE);
+      for (int dh = 0; dh < DH; ++dh)
+        tma_load_4d(q_smem + dh * HALF_ROWS, &q_map, bar_q, 0, kv_head * G, dh, q_begin + q0);
+    }
+    const int32_t* idx = p.kv_indices + ip0;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int s = tile & 1;
+      const int t0 = tile * kBN;
+      if (tile >= 2) {  // the stage's previous tile must have been consumed by the tensor core
+        if (!warp_wait(bar_kempty + 8 * s, ((tile >> 1) - 1) & 1, p.status) ||
+            !warp_wait(bar_vempty + 8 * s, ((tile >> 1) - 1) & 1, p.status)) {
+          *abort_flag = 1;
+          break;
+        }
+      }
+      int live = 0;  // boxes that hold at least one visible token
+      for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
+      if (lane == 0) {
+        mbar_expect_tx(bar_kfull + 8 * s, (uint32_t)(live * DH * bt * 128));
+        mbar_expect_tx(bar_vfull + 8 * s, (uint32_t)(live * DH * bt * 128));
+      }
+      __syncwarp();
+      for (int b = lane; b < n_boxes; b += 32) {
+        const int tok = t0 + b * bt;
+        if (tok >= kv_hi) continue;
+        int page = __ldg(idx + (tok >> ps_log));
+        if (page < 0 || page >= p.num_pages) {
+          record_status(p.status, ST_BAD_PAGE_ID);
+          page = 0;
+        }
+        const int in_page = tok & (ps - 1);
+        for (int dh = 0; dh < DH; ++dh) {
+          const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
+          tma_load_5d(k_smem + off, &kv_map, bar_kfull + 8 * s, 0, in_page, kv_head, dh, 2 * page);
+          tma_load_5d(v_smem + off, &kv_map, bar_vfull + 8 * s, 0, in_page, kv_head, dh, 2 * page + 1);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ================================ MMA issuer (one thread) ===================================
+    if (lane == 0) {
+      bool ok = mbar_wait(bar_q, 0, p.status);
+      auto issue_qk = [&](int tile) {  // S[tile & 1] = Q K_tile^T
+        const int s = tile & 1;
+        const uint32_t d = tmem + (s ? COL_S1 : COL_S0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t koff = (uint32_t)((kk >> 2) * HALF_ROWS + (kk & 3) * 32);
+          umma_ss(d, smem_desc(q_smem + koff, 16, 1024), smem_desc(k_smem + s * KVTILE + koff, 16, 1024), IDESC_QK,
+                  kk > 0 ? 1u : 0u);
+        }
+        tc_commit(bar_sfull + 8 * s);
+        tc_commit(bar_kempty + 8 * s);
+      };
+      if (ok) ok = mbar_wait(bar_kfull, 0, p.status);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int tile = 0; ok && tile < n_tiles; ++tile) {
+        const int s = tile & 1;
+        if (tile + 1 < n_tiles) {  // next S while the softmax warps work on this one
+          ok = mbar_wait(bar_kfull + 8 * (s ^ 1), ((tile + 1) >> 1) & 1, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(tile + 1);
+        }
+        ok = mbar_wait(bar_pfull, tile & 1, p.status) && mbar_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const int cols = min(kBN, kv_hi - tile * kBN);
+        const int ksteps = (cols + 15) >> 4;  // 16-token steps that hold a visible token
+        for (int kt = 0; kt < ksteps; ++kt)
+          umma_ts(tmem + COL_O, tmem + COL_P + kt * 8,
+                  smem_desc(v_smem + s * KVTILE + kt * 2048, HALF_ROWS, 1024), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
+        tc_commit(bar_odone);
+        tc_commit(bar_vempty + 8 * s);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    // ================================ softmax / correction / epilogue ============================
+    const int row = tid;                      // TMEM lane and MMA row
+    const int tok_local = row / G, head = row - tok_local * G;
+    const bool row_live = tok_local < nq;
+    // last kv position this row may see
+    const int limit = min(p.causal ? (kv_len - n_new + q0 + tok_local) : (kv_len - 1), kv_hi - 1);
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float sc = p.scale_log2;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int s = tile & 1;
+      if (!warp_wait(bar_sfull + 8 * s, (tile >> 1) & 1, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_base + (s ? COL_S1 : COL_S0);
+      const int t0 = tile * kBN;
+      const bool need_mask = (t0 + kBN - 1) > limit;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(r[i]);
+          if (need_mask && (t0 + c * 32 + i > limit)) x = -INFINITY;
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_tile = mx * sc;
+      // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 2^8
+      float factor = 1.f;
+      if (m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY)) {
+        factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_tile);
+        m_used = m_tile;
+      }
+      if (tile > 0) {  // O and P are free once the previous P.V has completed
+        if (!warp_wait(bar_odone, (tile - 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, factor != 1.f)) {
+          l *= factor;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + COL_O + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+            tmem_st32(tmem + lane_base + COL_O + c * 32, r);
+          }
+        }
+      }
+      // pass 2: P = exp2(S * scale - m_used), written to TMEM as 16-bit pairs
+      const float off = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float a = exp2f(fmaf(__uint_as_float(r[2 * i]), sc, -off));
+          float b = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), sc, -off));
+          if (need_mask) {
+            if (t0 + c * 32 + 2 * i > limit) a = 0.f;
+            if (t0 + c * 32 + 2 * i + 1 > limit) b = 0.f;
+          }
+          l += a + b;
+          pk[i] = pack2<T>(a, b);
+        }
+        tmem_st16(tmem + lane_base + COL_P + c * 16, pk);
+      }
+      tmem_wait_st();
+      // Rows of V past the visible length hold whatever the pool (or an older tile) left there;
+      // clear the ones inside the last issued 16-token step so that 0 * garbage stays 0.
+      const int cols = min(kBN, kv_hi - t0);
+      if (cols < kBN && (cols & 15) != 0) {
+        if (!warp_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status)) { ok = false; break; }
+        const int r0 = cols, r1 = (cols + 15) & ~15;
+        for (int x = tid; x < (r1 - r0) * DH * 8; x += 128) {
+          const int ch = x & 7, dh = (x >> 3) % DH, rr = r0 + (x >> 3) / DH;
+          *reinterpret_cast<uint4*>(smem + (v_smem - base) + s * KVTILE + dh * HALF_ROWS + rr * 128 + ch * 16) =
+              make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      }
+      tc_fence_before();
+      mbar_arrive(bar_pfull);
+    }
+    if (ok) ok = warp_wait(bar_odone, (n_tiles - 1) & 1, p.status);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* dst = reinterpret_cast<T*>(p.out) + (int64_t)(q_begin + q0 + tok_local) * p.out_stride +
+               (int64_t)(kv_head * G + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + COL_O + c * 32, r);
+        tmem_wait_ld();
+        if (row_live) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack2<T>(__uint_as_float(r[v * 8 + 2 * i]) * inv, __uint_as_float(r[v * 8 + 2 * i + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    } else {
+      *abort_flag = 1;
+    }
+  }
+
+  // ---- teardown: everyone meets here, then the allocating warp frees TMEM ----------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+// ---- host -------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+int ilog2_exact(int x) {
+  if (x <= 0 || (x & (x - 1)) != 0) return -1;
+  int l = 0;
+  while ((1 << l) < x) ++l;
+  return l;
+}
+
+}  // namespace
+}  // namespace dsv
+
+extern "C" {
+
+int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, int batch, int n_q_heads,
+                     int n_kv_heads, int head_dim, int page_size, int dtype, int causal, int32_t* plan_host,
+                     int64_t plan_capacity_i32, int64_t* plan_used_i32) {
+  using namespace dsv;
+  DSV_REQUIRE(qo_indptr_host && kv_len_host && plan_host && plan_used_i32, "prefill_plan: null pointer argument");
+  DSV_REQUIRE(batch >= 0, "prefill_plan: negative batch");
+  DSV_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "prefill_plan: bad head counts");
+  const int G = n_q_heads / n_kv_heads;
+  DSV_REQUIRE(G <= 128 && 128 % G == 0, "prefill_plan: GQA group %d must divide 128", G);
+  const int tq = 128 / G;
+  struct Item { int req, q0, nq, hi; };
+  std::vector<Item> items;
+  for (int i = 0; i < batch; ++i) {
+    const int n = qo_indptr_host[i + 1] - qo_indptr_host[i];
+    const int len = kv_len_host[i];
+    DSV_REQUIRE(n >= 0 && len >= n, "prefill_plan: request %d has %d new tokens but kv length %d", i, n, len);
+    for (int q0 = 0; q0 < n; q0 += tq) {
+      const int nq = std::min(tq, n - q0);
+      const int hi = causal ? len - n + q0 + nq : len;  // kv positions the tile's last token sees
+      items.push_back({i, q0, nq, hi});
+    }
+  }
+  const int64_t need = kPlanHeader + 4 * (int64_t)items.size();
+  *plan_used_i32 = need;
+  if (need > plan_capacity_i32)
+    return fail(DSV_E_WORKSPACE, "prefill_plan: plan needs %lld int32, capacity %lld", (long long)need,
+                (long long)plan_capacity_i32);
+  std::stable_sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.hi > b.hi; });
+  plan_host[0] = kPrefillMagic;
+  plan_host[1] = (int32_t)items.size();
+  plan_host[2] = tq;
+  plan_host[3] = causal ? 1 : 0;
+  plan_host[4] = batch;
+  plan_host[5] = kPlanHeader;
+  plan_host[6] = n_q_heads;
+  plan_host[7] = n_kv_heads;
+  for (size_t k = 0; k < items.size(); ++k) {
+    int32_t* it = plan_host + kPlanHeader + 4 * k;
+    it[0] = items[k].req; it[1] = items[k].q0; it[2] = items[k].nq; it[3] = items[k].hi;
+  }
+  (void)head_dim; (void)page_size; (void)dtype;
+  return DSV_OK;
+}
+
+int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_indptr, const void* pages_layer,
+                      int64_t page_stride, int64_t num_pages, const int32_t* kv_indices, const int32_t* kv_indptr,
+                      const int32_t* kv_last_page_len, void* out, int64_t out_stride_tok, const int32_t* plan_host,
+                      const int32_t* plan_dev, int batch, int nnz, int n_q_heads, int n_kv_heads, int head_dim,
+                      int page_size, int dtype, float sm_scale, int causal, void* stream) {
+  using namespace dsv;
+  DSV_REQUIRE(dtype_ok(dtype), "prefill: unknown dtype %d", dtype);
+  DSV_REQUIRE(batch >= 0 && nnz >= 0, "prefill: negative batch or nnz");
+  if (batch == 0 || nnz == 0) return DSV_OK;
+  DSV_REQUIRE(q && qo_indptr && pages_layer && kv_indices && kv_indptr && kv_last_page_len && out && plan_host && plan_dev,
+              "prefill: null pointer argument");
+  if (dtype == DSV_F32)
+    return fail(DSV_E_UNSUPPORTED, "prefill: fp32 K/V has no tensor-core kernel here (fp16 and bf16 only)");
+  DSV_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "prefill: bad head counts");
+  const int G = n_q_heads / n_kv_heads;
+  DSV_REQUIRE(G <= 128 && 128 % G == 0, "prefill: GQA group %d must divide 128", G);
+  DSV_REQUIRE(head_dim == 64 || head_dim == 128, "prefill: head_dim %d not in {64,128}", head_dim);
+  const int ps_log2 = ilog2_exact(page_size);
+  DSV_REQUIRE(ps_log2 >= 0, "prefill: page_size %d must be a power of two", page_size);
+  DSV_REQUIRE(num_pages > 0 && num_pages < (1ll << 30), "prefill: num_pages out of range");
+  DSV_REQUIRE(plan_host[0] == kPrefillMagic && plan_host[4] == batch && plan_host[6] == n_q_heads &&
+                  plan_host[7] == n_kv_heads && plan_host[3] == (causal ? 1 : 0),
+              "prefill: plan does not belong to this call");
+  DSV_REQUIRE(page_stride == (int64_t)2 * page_size * n_kv_heads * head_dim, "prefill: the page pool must be dense");
+  DSV_REQUIRE(aligned16(q) && aligned16(pages_layer) && aligned16(out) && (q_stride_tok * 2) % 16 == 0 &&
+                  (out_stride_tok * 2) % 16 == 0,
+              "prefill: pointers and strides must be 16-byte aligned");
+  DSV_REQUIRE(q_stride_tok >= (int64_t)n_q_heads * head_dim && out_stride_tok >= (int64_t)n_q_heads * head_dim,
+              "prefill: token stride smaller than a row");
+  const int n_items = plan_host[1];
+  if (n_items == 0) return DSV_OK;
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return fail(DSV_E_CUDA, "prefill: cuTensorMapEncodeTiled is not available");
+  const CUtensorMapDataType dt = dtype == DSV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  CUtensorMap q_map, kv_map;
+  {  // q: (64 elements, head, 64-element half, token); box = (64, G, 1, 128/G) -> rows token*G + head
+    const cuuint64_t dims[4] = {64, (cuuint64_t)n_q_heads, (cuuint64_t)(head_dim / 64), (cuuint64_t)nnz};
+    const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)q_stride_tok * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(128 / G)};
+    if (enc(&q_map, dt, 4, const_cast<void*>(q), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return fail(DSV_E_CUDA, "prefill: tensor map of q rejected");
+  }
+  {  // pages: (64 elements, token in page, head, 64-element half, 2*page + {K,V}); box = 16 tokens of one head and half
+    const int bt = page_size < 16 ? page_size : 16;
+    const cuuint64_t half_stride = (cuuint64_t)page_size * n_kv_heads * head_dim * 2;
+    const cuuint64_t dims[5] = {64, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, (cuuint64_t)(head_dim / 64),
+                                (cuuint64_t)(2 * num_pages)};
+    const cuuint64_t strides[4] = {(cuuint64_t)n_kv_heads * head_dim * 2, (cuuint64_t)head_dim * 2, 128, half_stride};
+    const cuuint32_t box[5] = {64, (cuuint32_t)bt, 1, 1, 1};
+    if (enc(&kv_map, dt, 5, const_cast<void*>(pages_layer), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return fail(DSV_E_CUDA, "prefill: tensor map of the pages rejected");
+  }
+  PrefillParams p;
+  p.qo_indptr = qo_indptr; p.kv_indices = kv_indices; p.kv_indptr = kv_indptr; p.kv_last_page_len = kv_last_page_len;
+  p.out = out; p.items = reinterpret_cast<const int4*>(plan_dev + plan_host[5]);
+  DSV_REQUIRE(aligned16(p.items), "prefill: device plan must be 16-byte aligned");
+  p.out_stride = out_stride_tok; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.ps_log2 = ps_log2;
+  p.num_pages = (int)num_pages; p.causal = causal ? 1 : 0; p.scale_log2 = sm_scale * kLog2e;
+  p.status = device_status_ptr();
+  const size_t smem = (size_t)128 * head_dim * 2 + 4 * (size_t)kBN * head_dim * 2 + 128 + 1024;
+  const dim3 grid((unsigned)n_items, (unsigned)n_kv_heads);
+  auto go = [&](auto kernel) -> cudaError_t {
+    cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (er != cudaSuccess) return er;
+    kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(q_map, kv_map, p);
+    return cudaGetLastError();
+  };
+  cudaError_t e;
+  if (dtype == DSV_BF16)
+    e = head_dim == 128 ? go(prefill_kernel<__nv_bfloat16, 128>) : go(prefill_kernel<__nv_bfloat16, 64>);
+  else
+    e = head_dim == 128 ? go(prefill_kernel<__half, 128>) : go(prefill_kernel<__half, 64>);
+  if (e != cudaSuccess) return fail(DSV_E_CUDA, "prefill launch failed: %s", cudaGetErrorString(e));
+  return DSV_OK;
+}
+
+}  // extern "C"

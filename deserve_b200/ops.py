@@ -204,3 +204,106 @@ class BatchDecodeWithPagedKVCacheWrapper:
 
     def end_forward(self) -> None:
         self._desc = None
+
+
+def prefill_plan_capacity(nnz: int, batch: int, group: int) -> int:
+    tq = max(1, 128 // group)
+    return _PLAN_HEADER + 4 * (nnz // tq + batch + 1)
+
+
+def make_prefill_plan(qo_indptr_host: np.ndarray, kv_len_host: np.ndarray, n_q_heads: int, n_kv_heads: int,
+                      head_dim: int, page_size: int, dtype: torch.dtype, causal: bool, plan_out: np.ndarray) -> int:
+    """Fill plan_out (int32) with the (request, q tile) work items; returns the int32 entries used."""
+    qo = np.ascontiguousarray(qo_indptr_host, dtype=np.int32)
+    kl = np.ascontiguousarray(kv_len_host, dtype=np.int32)
+    used = ctypes.c_int64()
+    _lib.check(_lib.lib.dsv_prefill_plan(qo.ctypes.data, kl.ctypes.data, len(kl), n_q_heads, n_kv_heads, head_dim,
+                                         page_size, _lib.dtype_code(dtype), 1 if causal else 0, plan_out.ctypes.data,
+                                         plan_out.size, ctypes.byref(used)))
+    return used.value
+
+
+def paged_prefill(q: torch.Tensor, qo_indptr: torch.Tensor, paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor,
+                  kv_indptr: torch.Tensor, kv_last_page_len: torch.Tensor, plan_host: np.ndarray,
+                  plan_dev: torch.Tensor, out: torch.Tensor | None = None, sm_scale: float | None = None,
+                  causal: bool = True) -> torch.Tensor:
+    """Functional form of the ragged causal prefill attention call: every buffer explicit."""
+    _lib.require_cuda(q, paged_kv_cache, plan_dev)
+    ps, hkv, d, page_stride = _pages_view(paged_kv_cache)
+    if q.dtype != paged_kv_cache.dtype:
+        raise ValueError("prefill: q dtype differs from the page dtype")
+    nnz, hq = q.shape[0], q.shape[1]
+    qs = _row_stride(q, hq, d, "q")
+    if out is None:
+        out = torch.empty((nnz, hq, d), dtype=q.dtype, device=q.device)
+    os_ = _row_stride(out, hq, d, "out")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    _lib.check(_lib.lib.dsv_paged_prefill(
+        q.data_ptr(), qs, qo_indptr.data_ptr(), paged_kv_cache.data_ptr(), page_stride, paged_kv_cache.shape[0],
+        kv_indices.data_ptr(), kv_indptr.data_ptr(), kv_last_page_len.data_ptr(), out.data_ptr(), os_,
+        plan_host.ctypes.data, plan_dev.data_ptr(), kv_last_page_len.shape[0], nnz, hq, hkv, d, ps,
+        _lib.dtype_code(q.dtype), float(sm_scale), 1 if causal else 0, _lib.current_stream_ptr(q.device)))
+    return out
+
+
+class BatchPrefillWithPagedKVCacheWrapper:
+    """begin_forward / forward / end_forward object of the reference's prefill path
+    (exec.py:22, 227-242; attention.py:188-192): ragged causal attention of the
+    step's new q rows against the paged K/V, also used for mixed prefill+decode
+    batches. The head of `workspace_buffer` holds the device copy of the plan."""
+
+    _PLAN_BYTES = 1 << 20
+
+    def __init__(self, workspace_buffer: torch.Tensor, kv_layout: str = "NHD"):
+        _lib.require_cuda(workspace_buffer)
+        if kv_layout != "NHD":
+            raise ValueError("only the NHD page layout of the reference is implemented")
+        if workspace_buffer.dtype != torch.uint8 or workspace_buffer.numel() < self._PLAN_BYTES:
+            raise ValueError("workspace_buffer must be a uint8 tensor of at least 1 MiB")
+        self._ws = workspace_buffer
+        self._plan_host: np.ndarray | None = None
+        self._pinned = None
+        self._desc = None
+
+    def begin_forward(self, qo_indptr: torch.Tensor, paged_kv_indptr: torch.Tensor, paged_kv_indices: torch.Tensor,
+                      paged_kv_last_page_len: torch.Tensor, num_qo_heads: int, num_kv_heads: int, head_dim: int,
+                      page_size: int, data_type=torch.float16, causal: bool = True, *,
+                      qo_indptr_host: np.ndarray | None = None, kv_indptr_host: np.ndarray | None = None,
+                      last_page_len_host: np.ndarray | None = None) -> None:
+        """Plan the q tiles of this batch. The *_host arrays (same values as the
+        device tensors) avoid three device->host copies."""
+        if qo_indptr_host is None:
+            qo_indptr_host = qo_indptr.cpu().numpy()
+        if kv_indptr_host is None:
+            kv_indptr_host = paged_kv_indptr.cpu().numpy()
+        if last_page_len_host is None:
+            last_page_len_host = paged_kv_last_page_len.cpu().numpy()
+        n_pages = np.diff(kv_indptr_host)
+        kv_len = np.where(n_pages > 0, (n_pages - 1) * page_size + last_page_len_host, 0).astype(np.int32)
+        batch, nnz = len(kv_len), int(qo_indptr_host[-1])
+        cap = prefill_plan_capacity(nnz, batch, num_qo_heads // num_kv_heads)
+        if cap * 4 > self._PLAN_BYTES:
+            raise _lib.DeserveKVError(f"prefill plan for {nnz} tokens does not fit the workspace head")
+        pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        dtype = data_type if isinstance(data_type, torch.dtype) else torch.float16
+        used = make_prefill_plan(qo_indptr_host, kv_len, num_qo_heads, num_kv_heads, head_dim, page_size, dtype, causal,
+                                 pinned.numpy())
+        self._ws[: used * 4].view(torch.int32).copy_(pinned[:used], non_blocking=True)
+        self._pinned, self._plan_host = pinned, pinned.numpy()
+        self._desc = (qo_indptr, paged_kv_indptr, paged_kv_indices, paged_kv_last_page_len, num_qo_heads, head_dim, causal)
+
+    def forward(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, causal: bool = True, sm_scale: float | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        if self._desc is None:
+            raise RuntimeError("forward() called outside begin_forward()/end_forward()")
+        qo, kv_indptr, kv_indices, last, hq, d, planned_causal = self._desc
+        if causal != planned_causal:
+            raise ValueError("forward(causal=...) differs from the value given to begin_forward")
+        if q.dim() == 2:
+            q = q.view(-1, hq, d)
+        return paged_prefill(q, qo, paged_kv_cache, kv_indices, kv_indptr, last, self._plan_host,
+                             self._ws[: self._PLAN_BYTES].view(torch.int32), out, sm_scale, causal)
+
+    def end_forward(self) -> None:
+        self._desc = None

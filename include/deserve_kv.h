@@ -139,6 +139,39 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
                      void* stream);
 
 /*
+ * Host-side planning for ragged causal paged prefill attention. Replaces
+ * BatchPrefillWithPagedKVCacheWrapper.begin_forward(...) at
+ * deserve_worker/execution/exec.py:227-236. Reads qo_indptr_host[batch+1] and
+ * kv_len_host[batch] (HOST memory; kv_len = post-append length of each
+ * request) and writes the list of (request, q-tile) work items: a tile holds
+ * 128 / (n_q_heads / n_kv_heads) q tokens and knows how many kv positions its
+ * last token sees (all of them when causal = 0). Pure host arithmetic.
+ */
+int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, int batch,
+                     int n_q_heads, int n_kv_heads, int head_dim, int page_size, int dtype,
+                     int causal, int32_t* plan_host, int64_t plan_capacity_i32,
+                     int64_t* plan_used_i32);
+
+/*
+ * Ragged causal attention of nnz new q rows against paged K/V (chunked
+ * prefill, and mixed prefill+decode batches) on the tcgen05 tensor cores. q
+ * row j (of n_i) of request i sees kv positions <= len_i - n_i + j (all
+ * positions when causal = 0). Replaces
+ * BatchPrefillWithPagedKVCacheWrapper.forward(xq, pages, causal=True) at
+ * deserve_worker/model/layer/attention.py:188-192. fp16 / bf16 only
+ * (DSV_E_UNSUPPORTED for fp32), head_dim 64 or 128, power-of-two page size,
+ * dense pool, GQA group dividing 128. fp32 softmax and accumulation; P is
+ * rounded to the 16-bit type before P.V, the output once at the end.
+ */
+int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_indptr,
+                      const void* pages_layer, int64_t page_stride, int64_t num_pages,
+                      const int32_t* kv_indices, const int32_t* kv_indptr,
+                      const int32_t* kv_last_page_len, void* out, int64_t out_stride_tok,
+                      const int32_t* plan_host, const int32_t* plan_dev, int batch, int nnz,
+                      int n_q_heads, int n_kv_heads, int head_dim, int page_size, int dtype,
+                      float sm_scale, int causal, void* stream);
+
+/*
  * dsv_paged_decode for callers that cannot allocate device memory. It has no
  * counterpart in the reference. Same arguments and results as dsv_paged_decode,
  * minus the workspace: the split-KV partial states live in a fixed scratch

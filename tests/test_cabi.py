@@ -100,3 +100,29 @@ def test_decode_plan_rejects_bad_input():
     plan = np.zeros(4, dtype=np.int32)
     with pytest.raises(_lib.DeserveKVError, match="plan needs"):
         ops.make_decode_plan(np.array([0, 5], dtype=np.int32), 8, 2, 64, 16, torch.float32, 148, plan)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_prefill_plan_tiles_every_new_token_once(causal):
+    qo = np.array([0, 100, 101, 613, 613, 650], dtype=np.int32)
+    kv_len = np.array([100, 900, 1024, 7, 37], dtype=np.int32)
+    plan = np.zeros(ops.prefill_plan_capacity(650, 5, 4), dtype=np.int32)
+    used = ops.make_prefill_plan(qo, kv_len, 32, 8, 128, 16, torch.bfloat16, causal, plan)
+    n_items, tq = plan[1], plan[2]
+    assert tq == 32 and used == 8 + 4 * n_items and plan[3] == int(causal)
+    items = plan[8:used].reshape(-1, 4)
+    cover = [np.zeros(n, dtype=int) for n in np.diff(qo)]
+    for req, q0, nq, hi in items:
+        assert 1 <= nq <= tq and q0 % tq == 0
+        cover[req][q0 : q0 + nq] += 1
+        n = qo[req + 1] - qo[req]
+        assert hi == (kv_len[req] - n + q0 + nq if causal else kv_len[req])
+    assert all((c == 1).all() for c in cover)
+    assert (np.diff(items[:, 3]) <= 0).all()  # most work first
+
+
+def test_prefill_plan_rejects_inconsistent_lengths():
+    plan = np.zeros(64, dtype=np.int32)
+    with pytest.raises(ValueError, match="new tokens"):
+        ops.make_prefill_plan(np.array([0, 50], dtype=np.int32), np.array([20], dtype=np.int32), 8, 2, 64, 16,
+                              torch.float16, True, plan)
