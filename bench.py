@@ -53,6 +53,11 @@ def parse_args():
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill attention measurement")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill measurement (profiling)")
+    ap.add_argument("--prefill-reqs", type=int, default=32)
+    ap.add_argument("--prefill-ctx", type=int, default=4096)
+    ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (BASELINE config 3)")
     ap.add_argument("--swap-seqs", type=int, default=64)
     ap.add_argument("--swap-tokens", type=int, default=2048)
@@ -229,6 +234,58 @@ def host_link_peak(dev, nbytes=1 << 30, reps=5):
     return out
 
 
+def prefill_measure(dk, args, dev, iters=5):
+    """Chunked-prefill attention (BASELINE config 5 shape): prefill_reqs requests that already hold
+    prefill_ctx tokens each get a chunk of prefill_chunk new tokens; ragged causal attention of the
+    chunk against the paged K/V on the tcgen05 kernel, one layer. Reports dense-equivalent TFLOP/s
+    (4 * Hq * D * visible (q, kv) pairs) against the measured bf16 GEMM peak."""
+    from deserve_b200 import ops
+
+    ps, hq, hkv, d = args.page_size, args.q_heads, args.kv_heads, args.head_dim
+    B, ctx, n = args.prefill_reqs, args.prefill_ctx, args.prefill_chunk
+    lens = np.full(B, ctx + n)
+    n_pages = (lens + ps - 1) // ps
+    total = int(n_pages.sum())
+    pool_pages = int(total * 1.25) + 1
+    g = torch.Generator(device=dev).manual_seed(7)
+    pages = torch.empty(pool_pages, 2, ps, hkv, d, dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    q = torch.randn(B * n, hq, d, device=dev, generator=g).to(torch.bfloat16)
+    qo = (np.arange(B + 1) * n).astype(np.int32)
+    kvp = np.concatenate([[0], np.cumsum(n_pages)]).astype(np.int32)
+    idx = np.random.default_rng(3).permutation(pool_pages)[:total].astype(np.int32)
+    last = ((lens - 1) % ps + 1).astype(np.int32)
+    plan = np.zeros(ops.prefill_plan_capacity(B * n, B, hq // hkv), dtype=np.int32)
+    used = ops.make_prefill_plan(qo, lens.astype(np.int32), hq, hkv, d, ps, torch.bfloat16, True, plan)
+    t = lambda a: torch.from_numpy(a).to(dev)
+    qo_d, kvp_d, idx_d, last_d, plan_d = t(qo), t(kvp), t(idx), t(last), t(plan[:used].copy())
+    out = torch.empty_like(q)
+
+    def run():
+        ops.paged_prefill(q, qo_d, pages, idx_d, kvp_d, last_d, plan, plan_d, out=out)
+
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    pairs = B * sum(ctx + j + 1 for j in range(n))
+    flops = 4.0 * hq * d * pairs
+    peak = 1646.8
+    try:
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except Exception:
+        peak = 1590.0
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"workload": f"{B} requests x ({ctx} context + {n}-token chunk), causal, 1 layer", "ms": ms,
+            "tflops": tf, "peak_tflops": peak, "frac": tf / peak, "prefill_tokens_per_s_per_layer": B * n / (ms * 1e-3),
+            "bound": "tensor"}
+
+
 def swap_stress(dk, pool, free_ids, args, dev, decode_step):
     """BASELINE config 3: the KV of swap_seqs x swap_tokens tokens, all layers, scattered over the
     permuted pool, is swapped out to pinned host chunks and back into DIFFERENT pages while decode
@@ -304,6 +361,10 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.prefill_only:
+        torch.cuda.set_device(local)
+        print(json.dumps({"prefill": prefill_measure(dk, args, torch.device("cuda", local))}), flush=True)
+        return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
@@ -482,6 +543,8 @@ def run_ours(args):
                          "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": e_ms / e2e_steps,
                          "api": "FlashDecodeCtx.init_paged_decode_ctx + BatchDecodeWithPagedKVCacheWrapper + "
                                 "append_paged_kv_cache, pinned host K/V/q in, pinned host out"}
+    if world == 1 and not args.no_prefill:
+        result["prefill"] = prefill_measure(dk, args, dev)
     if do_swap:
         result["swap"] = swap_stress(dk, pool, perm[at:], args, dev, lambda: stage.forward(
             q0[0], k_new[0], v_new[0], descs[(0, total_steps - 1)]))

@@ -52,7 +52,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
   for (int i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 128) __nanosleep(64);
+    if (i > (1 << 16)) __nanosleep(64);  // back off only when the wait is clearly not a normal one
   }
   record_status(status, ST_WAIT_TIMEOUT);
   return false;

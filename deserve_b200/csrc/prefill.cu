@@ -72,7 +72,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
   for (int i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 128) __nanosleep(64);
+    if (i > (1 << 16)) __nanosleep(64);  // back off only when the wait is clearly not a normal one
   }
   record_status(status, ST_WAIT_TIMEOUT);
   return false;
@@ -164,6 +164,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __host__ __device__ constexpr uint32_t instr_desc(int ab_format, int b_mn_major, int n, int m) {
   return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float ex2(float x) {  // 2^x on the special-function unit; ex2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <typename T>
@@ -261,38 +267,41 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         tma_load_4d(q_smem + dh * HALF_ROWS, &q_map, bar_q, 0, kv_head * G, dh, q_begin + q0);
     }
     const int32_t* idx = p.kv_indices + ip0;
+    bool failed = false;
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int s = tile & 1;
       const int t0 = tile * kBN;
-      if (tile >= 2) {  // the stage's previous tile must have been consumed by the tensor core
-        if (!warp_wait(bar_kempty + 8 * s, ((tile >> 1) - 1) & 1, p.status) ||
-            !warp_wait(bar_vempty + 8 * s, ((tile >> 1) - 1) & 1, p.status)) {
-          *abort_flag = 1;
-          break;
-        }
-      }
       int live = 0;  // boxes that hold at least one visible token
       for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
-      if (lane == 0) {
-        mbar_expect_tx(bar_kfull + 8 * s, (uint32_t)(live * DH * bt * 128));
-        mbar_expect_tx(bar_vfull + 8 * s, (uint32_t)(live * DH * bt * 128));
-      }
-      __syncwarp();
-      for (int b = lane; b < n_boxes; b += 32) {
-        const int tok = t0 + b * bt;
-        if (tok >= kv_hi) continue;
-        int page = __ldg(idx + (tok >> ps_log));
-        if (page < 0 || page >= p.num_pages) {
-          record_status(p.status, ST_BAD_PAGE_ID);
-          page = 0;
+      // K and V rings advance independently: the K stage is free as soon as Q K^T of two tiles
+      // ago has run (long before that tile's P V), so the next K tile is always in flight early
+      // and the MMA warp never waits for it.
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {
+        const uint32_t full = (kv ? bar_vfull : bar_kfull) + 8 * s, empty = (kv ? bar_vempty : bar_kempty) + 8 * s;
+        if (tile >= 2 && !warp_wait(empty, ((tile >> 1) - 1) & 1, p.status)) {
+          *abort_flag = 1;
+          failed = true;
+          break;
         }
-        const int in_page = tok & (ps - 1);
-        for (int dh = 0; dh < DH; ++dh) {
-          const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
-          tma_load_5d(k_smem + off, &kv_map, bar_kfull + 8 * s, 0, in_page, kv_head, dh, 2 * page);
-          tma_load_5d(v_smem + off, &kv_map, bar_vfull + 8 * s, 0, in_page, kv_head, dh, 2 * page + 1);
+        if (lane == 0) mbar_expect_tx(full, (uint32_t)(live * DH * bt * 128));
+        __syncwarp();
+        for (int b = lane; b < n_boxes; b += 32) {
+          const int tok = t0 + b * bt;
+          if (tok >= kv_hi) continue;
+          int page = __ldg(idx + (tok >> ps_log));
+          if (page < 0 || page >= p.num_pages) {
+            record_status(p.status, ST_BAD_PAGE_ID);
+            page = 0;
+          }
+          const int in_page = tok & (ps - 1);
+          for (int dh = 0; dh < DH; ++dh) {
+            const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
+            tma_load_5d((kv ? v_smem : k_smem) + off, &kv_map, full, 0, in_page, kv_head, dh, 2 * page + kv);
+          }
         }
       }
+      if (failed) break;
     }
   } else if (warp == 5) {
     // ================================ MMA issuer (one thread) ===================================
@@ -354,20 +363,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const uint32_t s_addr = tmem + lane_base + (s ? COL_S1 : COL_S0);
       const int t0 = tile * kBN;
       const bool need_mask = (t0 + kBN - 1) > limit;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_wait_ld();
+      // the whole S row in registers: four 32-column loads in flight, one wait
+      uint32_t r[kBN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(r[i]);
-          if (need_mask && (t0 + c * 32 + i > limit)) x = -INFINITY;
-          mx = fmaxf(mx, x);
-        }
+      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_wait_ld();
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < kBN; ++i)
+          if (t0 + i > limit) r[i] = 0xff800000u;  // -inf
       }
+#pragma unroll
+      for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
       const float m_tile = mx * sc;
       // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 2^8
       float factor = 1.f;
@@ -382,36 +390,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           l *= factor;
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + COL_O + c * 32, r);
+            uint32_t o[32];
+            tmem_ld32(tmem + lane_base + COL_O + c * 32, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-            tmem_st32(tmem + lane_base + COL_O + c * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st32(tmem + lane_base + COL_O + c * 32, o);
           }
         }
       }
-      // pass 2: P = exp2(S * scale - m_used), written to TMEM as 16-bit pairs
+      // P = exp2(S * scale - m_used) (masked entries are exp2(-inf) = 0), written to TMEM as 16-bit pairs
       const float off = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
       for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float a = exp2f(fmaf(__uint_as_float(r[2 * i]), sc, -off));
-          float b = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), sc, -off));
-          if (need_mask) {
-            if (t0 + c * 32 + 2 * i > limit) a = 0.f;
-            if (t0 + c * 32 + 2 * i + 1 > limit) b = 0.f;
-          }
-          l += a + b;
+          const float a = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i]), sc, -off));
+          const float b = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i + 1]), sc, -off));
+          l0 += a;
+          l1 += b;
           pk[i] = pack2<T>(a, b);
         }
         tmem_st16(tmem + lane_base + COL_P + c * 16, pk);
       }
+      l += l0 + l1;
       tmem_wait_st();
       // Rows of V past the visible length hold whatever the pool (or an older tile) left there;
       // clear the ones inside the last issued 16-token step so that 0 * garbage stays 0.
