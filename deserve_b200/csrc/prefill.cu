@@ -30,7 +30,7 @@ namespace dsv {
 namespace {
 
 constexpr int kBN = 128;                 // kv tokens per tile
-constexpr int kThreads = 192;            // 4 softmax warps, producer warp, MMA warp
+constexpr int kThreads = 224;            // 4 softmax warps, K producer, MMA warp, V producer
 constexpr int kSpinLimit = 1 << 21;
 constexpr int32_t kPrefillMagic = 0x44535032;  // "DSP2"
 constexpr int kPlanHeader = 8;
@@ -259,9 +259,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4) {
-    // ================================ TMA producer =============================================
-    if (lane == 0) {
+  if (warp == 4 || warp == 6) {
+    // ================================ TMA producers: warp 4 = q + K ring, warp 6 = V ring =============================================
+    if (warp == 4 && lane == 0) {
       mbar_expect_tx(bar_q, QTILE);
       for (int dh = 0; dh < DH; ++dh)
         tma_load_4d(q_smem + dh * HALF_ROWS, &q_map, bar_q, 0, kv_head * G, dh, q_begin + q0);
@@ -276,8 +276,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       // K and V rings advance independently: the K stage is free as soon as Q K^T of two tiles
       // ago has run (long before that tile's P V), so the next K tile is always in flight early
       // and the MMA warp never waits for it.
-#pragma unroll
-      for (int kv = 0; kv < 2; ++kv) {
+      {
+        const int kv = warp == 6 ? 1 : 0;
         const uint32_t full = (kv ? bar_vfull : bar_kfull) + 8 * s, empty = (kv ? bar_vempty : bar_kempty) + 8 * s;
         if (tile >= 2 && !warp_wait(empty, ((tile >> 1) - 1) & 1, p.status)) {
           *abort_flag = 1;
