@@ -11,6 +11,9 @@ from .kvcache import (ChunkHandle, ChunkPool, CopiedPinnedMemory, CpuChunkPool, 
                       VirtualPagedKVCache, VirtualPagePool)
 from .ops import (BatchDecodeWithPagedKVCacheWrapper, BatchPrefillWithPagedKVCacheWrapper, append_paged_kv_cache,
                   apply_rope, apply_rope_inplace, paged_decode, paged_prefill)
+from .engine import (BatchDecode, BatchPrefill, BatchResult, KVStage, MicroBatchProcessor, RingPipeline, StageProcessor,
+                     StepRequest)
+from .model import LlamaStage, ModelArgs
 from .task import SamplingParams, TaskData, TaskManager
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -149,3 +149,262 @@ class RingPipeline:
             else:
                 self.inbox = y
             self.slot += 1
+
+
+# =================================================================================================
+# Engine-facing classes with the reference's names and call order
+# =================================================================================================
+from dataclasses import field as _field  # noqa: E402
+
+from .context import FlashPrefillCtx  # noqa: E402
+from .kvcache import ChunkHandle, KVCacheManager, PageTableAllocator, VirtualPagedKVCache, CopiedPinnedMemory  # noqa: E402
+from .task import SamplingParams, TaskManager  # noqa: E402
+
+
+@dataclass
+class BatchResult:
+    """deserve_worker/execution/result.py:6-13."""
+
+    ongoing_xs: torch.Tensor
+    ongoing_task_ids: list
+    all_xs: torch.Tensor
+    all_task_ids: list
+    done_task_ids: list
+    needed_probs: dict
+
+
+_WRAPPERS: dict = {}
+
+
+def stage_wrappers(device) -> tuple:
+    """One 128 MiB workspace and one decode + one prefill wrapper per device (the
+    reference creates them at import time, deserve_worker/execution/exec.py:20-22)."""
+    key = torch.device(device).index or 0
+    if key not in _WRAPPERS:
+        ws = torch.empty(128 << 20, dtype=torch.uint8, device=device)
+        ws2 = torch.empty(2 << 20, dtype=torch.uint8, device=device)
+        _WRAPPERS[key] = (ops.BatchDecodeWithPagedKVCacheWrapper(ws), ops.BatchPrefillWithPagedKVCacheWrapper(ws2))
+    return _WRAPPERS[key]
+
+
+@dataclass
+class BatchExec:
+    """deserve_worker/execution/exec.py:58-147 (the parts the microbatch path uses)."""
+
+    xs: torch.Tensor
+    layer_storage: object
+    task_datas: list
+    kvcaches: list
+
+    def bsz(self) -> int:
+        return len(self.task_datas)
+
+    def seqlens(self) -> list:
+        return [t.seqlen for t in self.task_datas]
+
+    def total_seqlen(self) -> int:
+        return sum(self.seqlens())
+
+    def post_process(self, result: torch.Tensor, ignore_eos: bool) -> BatchResult:
+        ids = [t.task_id for t in self.task_datas]
+        if not self.layer_storage.need_sample:
+            return BatchResult(result, ids, result, ids, [], {})
+        tokens, produced, done = self.layer_storage.sample(result, self.task_datas, ignore_eos)
+        all_idx = [i for i, p in enumerate(produced) if p]
+        on_idx = [i for i in all_idx if ids[i] not in done]
+        pick = lambda idx: tokens[torch.as_tensor(idx, dtype=torch.long, device=tokens.device)] if idx else tokens[:0]
+        return BatchResult(pick(on_idx), [ids[i] for i in on_idx], pick(all_idx), [ids[i] for i in all_idx], list(done), {})
+
+
+@dataclass
+class BatchDecode(BatchExec):
+    """All rows have seqlen 1 (exec.py:150-199)."""
+
+    decode_ctx: Optional[FlashDecodeCtx] = None
+
+    def prepare(self) -> None:
+        wrapper, _ = stage_wrappers(self.kvcaches[0].pool.main_device)
+        self.decode_ctx = FlashDecodeCtx.init_paged_decode_ctx(self.task_datas, self.kvcaches, wrapper)
+        a, c = self.layer_storage.model_args, self.decode_ctx
+        wrapper.begin_forward(indptr=c.kv_page_indptr, indices=c.kv_page_indices, last_page_len=c.kv_last_page_lens,
+                              num_qo_heads=a.n_heads, num_kv_heads=a.n_kv_heads, head_dim=a.dim // a.n_heads,
+                              page_size=c.page_pool.page_size, data_type=c.page_pool.main_dtype,
+                              indptr_host=c.host["kv_page_indptr"])
+
+    def step(self, ignore_eos: bool) -> BatchResult:
+        with torch.inference_mode():
+            result = self.layer_storage.forward(self.xs, self.decode_ctx)
+            self.decode_ctx.decode_wrapper.end_forward()
+            return self.post_process(result, ignore_eos)
+
+
+@dataclass
+class BatchPrefill(BatchExec):
+    """Prompt chunks, possibly mixed with decode rows (exec.py:202-243)."""
+
+    prefill_ctx: Optional[FlashPrefillCtx] = None
+
+    def prepare(self) -> None:
+        _, wrapper = stage_wrappers(self.kvcaches[0].pool.main_device)
+        self.prefill_ctx = FlashPrefillCtx.init_paged_prefill_ctx(self.task_datas, self.kvcaches, wrapper)
+        a, c = self.layer_storage.model_args, self.prefill_ctx
+        wrapper.begin_forward(qo_indptr=c.indptr, paged_kv_indptr=c.kv_page_indptr, paged_kv_indices=c.kv_page_indices,
+                              paged_kv_last_page_len=c.kv_last_page_lens, num_qo_heads=a.n_heads,
+                              num_kv_heads=a.n_kv_heads, head_dim=a.dim // a.n_heads, page_size=c.page_pool.page_size,
+                              data_type=c.page_pool.main_dtype, causal=True, qo_indptr_host=c.host["indptr"],
+                              kv_indptr_host=c.host["kv_page_indptr"], last_page_len_host=c.host["kv_last_page_lens"])
+
+    def step(self, ignore_eos: bool) -> BatchResult:
+        with torch.inference_mode():
+            result = self.layer_storage.forward(self.xs, self.prefill_ctx)
+            self.prefill_ctx.prefill_wrapper.end_forward()
+            return self.post_process(result, ignore_eos)
+
+
+class MicroBatchProcessor:
+    """One microbatch: its tasks' KV caches and the pinned image of its swap
+    region (deserve_worker/engine/microbatch/processor.py:24-149)."""
+
+    def __init__(self, kvcache_manager: KVCacheManager, task_data_manager: TaskManager, layer_storage,
+                 page_table_allocator: PageTableAllocator, ignore_eos: bool) -> None:
+        self.kvcache_manager = kvcache_manager
+        pool = kvcache_manager.virtual_page_pool
+        self.pinned_memory = CopiedPinnedMemory(size=pool.calc_swap_size(), num_pages_swap=pool.num_pages_swap,
+                                                device=pool.main_device, dtype=pool.main_dtype)
+        self.task_data_manager = task_data_manager
+        self.layer_storage = layer_storage
+        self.ongoing_paged_kvcaches: dict = {}
+        self.ignore_eos = ignore_eos
+        self.page_table_allocator = page_table_allocator
+
+    def join(self, task_ids: list) -> None:
+        for task_id in task_ids:
+            self.ongoing_paged_kvcaches[task_id] = VirtualPagedKVCache.empty(
+                self.page_table_allocator, self.kvcache_manager.virtual_page_pool)
+
+    def adjust(self) -> None:
+        vpp = self.kvcache_manager.virtual_page_pool
+        offset = vpp.num_pages_swap if vpp.on == 1 else -vpp.num_pages_swap
+        for kv in self.ongoing_paged_kvcaches.values():
+            kv.adjust(offset)
+
+    def offload(self, task_ids: list) -> list:
+        """Tasks leave the device: one pipelined transfer for all of them, then
+        their pages and table rows are freed."""
+        kvs = [self.ongoing_paged_kvcaches.pop(t) for t in task_ids]
+        handles = self.kvcache_manager.offload_many(kvs) if kvs else []
+        for kv in kvs:
+            kv.free()
+        return handles
+
+    def reload(self, task_ids: list, cpu_chunk_handles: list) -> None:
+        kvs = self.kvcache_manager.reload_many(cpu_chunk_handles) if cpu_chunk_handles else []
+        for task_id, kv in zip(task_ids, kvs):
+            self.ongoing_paged_kvcaches[task_id] = kv
+        for h in cpu_chunk_handles:
+            h.free()
+
+    def cancel(self, task_ids: list) -> None:
+        for task_id in task_ids:
+            kv = self.ongoing_paged_kvcaches.pop(task_id, None)
+            if kv is not None:
+                kv.free()
+
+    def _batch(self, task_ids: list, xs: torch.Tensor):
+        task_datas = [self.task_data_manager.get(t) for t in task_ids]
+        kvcaches = [self.ongoing_paged_kvcaches[t] for t in task_ids]
+        cls = BatchDecode if all(t.seqlen == 1 for t in task_datas) else BatchPrefill
+        return cls(xs, self.layer_storage, task_datas, kvcaches)
+
+    def exec(self, xs: torch.Tensor, task_ids: list) -> BatchResult:
+        batch = self._batch(task_ids, xs)
+        batch.prepare()
+        return batch.step(self.ignore_eos)
+
+    def step(self, task_ids: list, xs: torch.Tensor, prev_group: "MicroBatchProcessor",
+             next_group: "MicroBatchProcessor") -> BatchResult:
+        """prepare (grow caches, descriptors, plan) -> start the region swap for the
+        neighbours on the side streams -> run the layers (processor.py:107-146)."""
+        batch = self._batch(task_ids, xs)
+        batch.prepare()
+        pool = self.kvcache_manager.virtual_page_pool
+        if pool.num_pages_swap > 0:
+            pool.swap2(next_group.pinned_memory, prev_group.pinned_memory)
+        return batch.step(self.ignore_eos)
+
+    def synchronize(self) -> None:
+        self.kvcache_manager.synchronize()
+
+
+@dataclass
+class StepRequest:
+    """The fields of deserve_worker/request.py:137-213 that drive a stage."""
+
+    microbatch_id: int
+    xs: torch.Tensor
+    exec_task_ids: list = _field(default_factory=list)
+    exec_seqlens: list = _field(default_factory=list)
+    cancel_task_ids: list = _field(default_factory=list)
+    offload_task_ids: list = _field(default_factory=list)
+    reload_task_ids: list = _field(default_factory=list)
+    init_tasks: dict = _field(default_factory=dict)  # task id -> (prompt length, SamplingParams)
+
+
+class StageProcessor:
+    """The per-stage ordering contract of the reference's PipelineProcessor
+    (deserve_worker/engine/pipeline/processor.py:226-301) without its HTTP shell:
+    synchronize() = wait for the region DMA + switch(); process_step() = (adjust)
+    -> init seqlens -> cancel -> offload -> reload -> synchronize the manager ->
+    join -> step (prepare, swap2, layers) -> TaskData.step."""
+
+    def __init__(self, kvcache_manager: KVCacheManager, task_manager: TaskManager, layer_storage,
+                 page_table_allocator: PageTableAllocator, num_rounds: int, ignore_eos: bool = True):
+        self.kvcache_manager, self.task_manager, self.layer_storage = kvcache_manager, task_manager, layer_storage
+        self.num_rounds = num_rounds
+        self.microbatches = [MicroBatchProcessor(kvcache_manager, task_manager, layer_storage, page_table_allocator,
+                                                 ignore_eos) for _ in range(num_rounds)]
+        self.offloaded_kvcaches: dict = {}
+        self.current_microbatch_id = 0
+
+    def synchronize(self) -> None:
+        pool = self.kvcache_manager.virtual_page_pool
+        if pool.stream is not None:
+            pool.stream.synchronize()
+            pool.stream2.synchronize()
+        pool.switch()
+
+    def process_step(self, request: StepRequest) -> tuple:
+        mb = self.microbatches[request.microbatch_id]
+        assert request.microbatch_id == self.current_microbatch_id
+        self.current_microbatch_id = (self.current_microbatch_id + 1) % self.num_rounds
+        if self.num_rounds % 2 == 1:
+            mb.adjust()
+        prev_mb = self.microbatches[(request.microbatch_id - 1) % self.num_rounds]
+        next_mb = self.microbatches[(request.microbatch_id + 1) % self.num_rounds]
+        for task_id, (prompt_len, sp) in request.init_tasks.items():
+            if task_id not in self.task_manager.task_datas:
+                self.task_manager.add(TaskData.empty(task_id, prompt_len, sp))
+        for task_id, seqlen in zip(request.exec_task_ids, request.exec_seqlens):
+            self.task_manager.get(task_id).init(seqlen)
+        mb.cancel(request.cancel_task_ids)
+        for task_id, h in zip(request.offload_task_ids, mb.offload(request.offload_task_ids)):
+            self.offloaded_kvcaches[task_id] = h
+        mb.reload(request.reload_task_ids, [self.offloaded_kvcaches.pop(t) for t in request.reload_task_ids])
+        mb.kvcache_manager.synchronize()
+        result = None
+        if request.exec_task_ids:
+            mb.join([t for t in request.init_tasks if t not in mb.ongoing_paged_kvcaches])
+            result = mb.step(request.exec_task_ids, request.xs, prev_mb, next_mb)
+            for task_id in request.exec_task_ids:
+                self.task_manager.get(task_id).step()
+            if self.layer_storage.need_sample:
+                request.cancel_task_ids = result.done_task_ids
+            request.xs = result.ongoing_xs
+            request.exec_task_ids = result.ongoing_task_ids
+        else:
+            pool = self.kvcache_manager.virtual_page_pool
+            if pool.num_pages_swap > 0:  # an idle slot keeps the region rotation going
+                pool.swap2(next_mb.pinned_memory, prev_mb.pinned_memory)
+            if self.layer_storage.need_sample:
+                request.cancel_task_ids = []
+        return request, result

@@ -1,0 +1,146 @@
+"""A random-init Llama stage that drives the KV path the way the reference's
+layers do (deserve_worker/model/llama.py:53-88, model/layer/attention.py:126-193,
+layer/norm.py:21-34, layer/linear.py:115-123, looped by
+LayerStorage.forward, deserve_worker/layer_storage.py:182-197).
+
+It plays the role of the reference's LayerStorage for the engine classes: it has
+`forward(h, ctx)`, `need_sample`, `need_tokenize`, `model_args` and a greedy
+`sample`. Dense projections are torch matmuls (cuBLAS); RoPE, append and paged
+attention are this package's kernels. Weights are N(0, 0.02) from a per-layer
+seed, so any split of the layers over stages sees the same model.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+from .context import FlashDecodeCtx, FlashForwardCtx, FlashPrefillCtx
+from .task import TaskData
+
+
+@dataclass
+class ModelArgs:
+    dim: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    vocab_size: int = 128256
+    ffn_dim: int = 14336
+    norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    page_size: int = 16
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+
+llama_3_8b_args = ModelArgs()
+llama_3_70b_args = ModelArgs(dim=8192, n_layers=80, n_heads=64, n_kv_heads=8, ffn_dim=28672)
+
+
+def init_weight(shape, seed: int, device, dtype, std: float = 0.02) -> torch.Tensor:
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    if torch.device(device).type == "cpu" or shape[0] * shape[1] <= (1 << 22):
+        return (torch.randn(shape, generator=g) * std).to(dtype).to(device)
+    # large matrices: drawn on the device, row block by row block, from seeds derived from `seed`
+    out = torch.empty(shape, dtype=dtype, device=device)
+    gd = torch.Generator(device=device)
+    rows = max(1, (1 << 24) // shape[1])
+    for i, r0 in enumerate(range(0, shape[0], rows)):
+        gd.manual_seed(seed * 1000003 + i)
+        blk = out[r0 : r0 + rows]
+        blk.copy_((torch.randn(blk.shape, generator=gd, device=device) * std).to(dtype))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+
+
+class LlamaStage:
+    """Layers [layer_begin, layer_end) of the model; the first stage also embeds
+    tokens, the last one also applies the final norm and the output projection."""
+
+    def __init__(self, args: ModelArgs, layer_begin: int, layer_end: int, device, dtype, seed: int = 0,
+                 first: bool | None = None, last: bool | None = None):
+        self.model_args = args
+        self.layer_begin, self.layer_end = layer_begin, layer_end
+        self.need_tokenize = layer_begin == 0 if first is None else first
+        self.need_sample = layer_end == args.n_layers if last is None else last
+        self.main_device, self.dtype = torch.device(device), dtype
+        a, hd = args, args.head_dim
+        qkv_rows = (a.n_heads + 2 * a.n_kv_heads) * hd
+        self.layers = []
+        for l in range(layer_begin, layer_end):
+            s = seed * 7919 + l * 16
+            self.layers.append({
+                "wqkv": init_weight((qkv_rows, a.dim), s + 1, device, dtype),
+                "wo": init_weight((a.dim, a.n_heads * hd), s + 2, device, dtype),
+                "w13": init_weight((2 * a.ffn_dim, a.dim), s + 3, device, dtype),
+                "w2": init_weight((a.dim, a.ffn_dim), s + 4, device, dtype),
+                "attn_norm": torch.ones(a.dim, dtype=dtype, device=device),
+                "ffn_norm": torch.ones(a.dim, dtype=dtype, device=device),
+            })
+        if self.need_tokenize:
+            self.tok_embeddings = init_weight((a.vocab_size, a.dim), seed * 7919 + 900001, device, dtype)
+        if self.need_sample:
+            self.norm = torch.ones(a.dim, dtype=dtype, device=device)
+            self.output = init_weight((a.vocab_size, a.dim), seed * 7919 + 900002, device, dtype)
+
+    # ---- one transformer block --------------------------------------------------------------
+    def _block(self, w: dict, x: torch.Tensor, ctx: FlashForwardCtx) -> torch.Tensor:
+        a, hd = self.model_args, self.model_args.head_dim
+        qkv = rmsnorm(x, w["attn_norm"], a.norm_eps) @ w["wqkv"].t()
+        nq, nkv = a.n_heads * hd, a.n_kv_heads * hd
+        q = qkv[:, :nq].unflatten(1, (a.n_heads, hd))
+        k = qkv[:, nq : nq + nkv].unflatten(1, (a.n_kv_heads, hd))
+        v = qkv[:, nq + nkv :].unflatten(1, (a.n_kv_heads, hd))
+        ops.apply_rope_inplace(q, k, ctx.indptr, ctx.offsets, True, a.rope_theta)
+        pages = ctx.page_pool.get_layered_pages(ctx.layer_id)
+        ops.append_paged_kv_cache(k, v, ctx.indptr, pages, ctx.kv_page_indices, ctx.kv_page_indptr,
+                                  ctx.kv_last_page_lens)
+        if isinstance(ctx, FlashDecodeCtx):
+            attn = ctx.decode_wrapper.forward(q, pages)
+        else:
+            assert isinstance(ctx, FlashPrefillCtx)
+            attn = ctx.prefill_wrapper.forward(q, pages, causal=True)
+        h = x + attn.view(-1, nq) @ w["wo"].t()
+        gu = rmsnorm(h, w["ffn_norm"], a.norm_eps) @ w["w13"].t()
+        gate, up = gu[:, : a.ffn_dim], gu[:, a.ffn_dim :]
+        return h + (torch.nn.functional.silu(gate) * up) @ w["w2"].t()
+
+    @torch.inference_mode()
+    def forward(self, h: torch.Tensor, ctx: FlashForwardCtx) -> torch.Tensor:
+        """h: token ids [nnz] on the first stage, activations [nnz, dim] otherwise.
+        Returns activations, or on the last stage the logits of every request's
+        last row [bsz, vocab]."""
+        if self.need_tokenize:
+            h = self.tok_embeddings[h.long()]
+        for w in self.layers:
+            h = self._block(w, h, ctx)
+            ctx.layer_id += 1
+        if self.need_sample:
+            last_rows = (ctx.indptr[1:] - 1).long()
+            h = rmsnorm(h[last_rows], self.norm, self.model_args.norm_eps) @ self.output.t()
+        return h
+
+    @torch.inference_mode()
+    def sample(self, logits: torch.Tensor, task_datas: list[TaskData], ignore_eos: bool):
+        """Greedy next token of every request that finished its prompt (one batched
+        argmax and one device->host copy instead of the reference's per-task
+        argmax + cat, layer_storage.py:219-253). Returns (tokens [bsz] int32 on the
+        device, mask of requests that produced a token, ids done)."""
+        tokens = torch.argmax(logits.float(), dim=-1).to(torch.int32)
+        produced, done = [], []
+        for t in task_datas:
+            fin = t.finished_prefill()
+            produced.append(fin)
+            if fin:
+                t.sampling_params.max_new_tokens -= 1
+                if t.sampling_params.max_new_tokens <= 0 or t.start_pos >= t.sampling_params.max_seq_len:
+                    done.append(t.task_id)
+        return tokens, produced, done

@@ -1,0 +1,112 @@
+"""The engine classes (MicroBatchProcessor / StageProcessor, the reference's
+process_step ordering) driving a random-init Llama stage end to end on the GPU:
+chunked prefill, mixed batches, decode, three microbatches rotating through the
+two swap regions (odd count, so page tables are shifted by adjust), and a task
+offloaded to pinned host memory and reloaded into other pages. Greedy tokens are
+checked against a dense fp32 CPU model with the same weights."""
+import pytest
+import torch
+
+import deserve_b200 as dk
+from deserve_b200 import _lib
+from oracle.llama_ref import DenseLlama
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _setup(dtype, rounds, main_pages, swap_pages):
+    args = dk.ModelArgs(dim=512, n_layers=3, n_heads=8, n_kv_heads=2, vocab_size=640, ffn_dim=1024, page_size=16)
+    stage = dk.LlamaStage(args, 0, args.n_layers, DEV, dtype, seed=3)
+    # decisive logits: the comparison is about the KV path, not about ties of a flat distribution
+    stage.output.mul_(12.0)
+    pool = dk.VirtualPagePool(args.n_layers, main_pages, swap_pages, args.page_size, DEV, dtype,
+                              n_kv_heads=args.n_kv_heads, head_dim=args.head_dim)
+    pool.pages.fill_(float("nan"))  # anything read but never written shows up at once
+    pta = dk.PageTableAllocator(32, 2048, args.page_size, DEV)
+    chunks = dk.CpuChunkPool(args.n_layers, 7, args.page_size, dtype, n_kv_heads=args.n_kv_heads, head_dim=args.head_dim)
+    mgr = dk.KVCacheManager(pool, chunks, pta)
+    tm = dk.TaskManager(pool.num_pages, args.page_size)
+    proc = dk.StageProcessor(mgr, tm, stage, pta, rounds, ignore_eos=True)
+    ref = DenseLlama(args, stage.layers, stage.tok_embeddings, stage.norm, stage.output)
+    return args, proc, ref, pool
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_engine_greedy_tokens_match_dense_reference(dtype):
+    rounds, chunk, steps = 3, 48, 10
+    args, proc, ref, pool = _setup(dtype, rounds, main_pages=24, swap_pages=12)
+    g = torch.Generator().manual_seed(11)
+    prompts = {}
+    for mb in range(rounds):
+        for j, n in enumerate([5, 70, 33][: 3 - (mb == 2)]):
+            prompts[f"m{mb}t{j}"] = torch.randint(1, args.vocab_size, (n + 7 * mb,), generator=g, dtype=torch.int32)
+    fed = {t: 0 for t in prompts}          # prompt tokens already in the cache
+    last_tok = {}                           # last generated token of tasks that are decoding
+    generated = {t: [] for t in prompts}
+    offloaded, mismatches, checked = set(), [], 0
+    for it in range(steps + 3):
+        for mb in range(rounds):
+            ids = [t for t in prompts if t.startswith(f"m{mb}")]
+            req = dk.StepRequest(microbatch_id=mb, xs=torch.empty(0, dtype=torch.int32, device=DEV))
+            # one task of microbatch 0 sits out two rounds on the host
+            if mb == 0 and it == 5:
+                req.offload_task_ids = ["m0t1"]
+                offloaded.add("m0t1")
+            if mb == 0 and it == 7:
+                req.reload_task_ids = ["m0t1"]
+                offloaded.discard("m0t1")
+            xs = []
+            for t in ids:
+                if t in offloaded:
+                    continue
+                if fed[t] < len(prompts[t]):
+                    n = min(chunk, len(prompts[t]) - fed[t])
+                    xs.append(prompts[t][fed[t] : fed[t] + n])
+                    if fed[t] == 0:
+                        req.init_tasks[t] = (len(prompts[t]), dk.SamplingParams())
+                    req.exec_seqlens.append(n)
+                else:
+                    xs.append(torch.tensor([last_tok[t]], dtype=torch.int32))
+                    req.exec_seqlens.append(1)
+                req.exec_task_ids.append(t)
+            req.xs = torch.cat(xs).to(DEV) if xs else req.xs
+            exec_ids, seqlens, fed_tokens = list(req.exec_task_ids), list(req.exec_seqlens), xs
+            proc.synchronize()
+            _, result = proc.process_step(req)
+            if result is None:
+                continue
+            got = dict(zip(result.all_task_ids, result.all_xs.cpu().tolist()))
+            for t, n, toks in zip(exec_ids, seqlens, fed_tokens):
+                want = ref.step(t, toks)
+                if fed[t] < len(prompts[t]):
+                    fed[t] += n
+                if fed[t] >= len(prompts[t]):  # produced a token
+                    assert t in got, f"{t} finished its prompt but produced no token"
+                    checked += 1
+                    if got[t] != want:
+                        gap = float(ref.last_logits[want] - ref.last_logits[got[t]])
+                        mismatches.append((t, it, got[t], want, gap))
+                    last_tok[t] = got[t]
+                    generated[t].append(got[t])
+                else:
+                    assert t not in got
+    assert checked >= 8 * steps
+    # identical greedy tokens; a differing token is only tolerated as a tie within 16-bit resolution
+    assert all(gap < 0.05 for *_, gap in mismatches), mismatches
+    assert len(mismatches) <= checked // 50, mismatches
+    assert _lib.read_device_status() == 0
+    assert not pool.pages[:, : pool.num_pages_main].isnan().all()  # the pool was really used
+
+
+def test_microbatch_processor_api_and_errors():
+    args, proc, ref, pool = _setup(torch.bfloat16, 2, main_pages=6, swap_pages=2)
+    mb = proc.microbatches[0]
+    mb.join(["a", "b"])
+    assert set(mb.ongoing_paged_kvcaches) == {"a", "b"}
+    proc.task_manager.add(dk.TaskData.empty("a", 200))
+    proc.task_manager.get("a").init(200)
+    with pytest.raises(ValueError, match="Not enough pages"):  # 13 pages needed, 8 available
+        mb.step(["a"], torch.zeros(200, dtype=torch.int32, device=DEV), proc.microbatches[1], proc.microbatches[1])
+    mb.cancel(["a", "b", "never-joined"])
+    assert not mb.ongoing_paged_kvcaches and pool.num_avails == 8
