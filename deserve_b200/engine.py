@@ -101,7 +101,11 @@ class RingPipeline:
     first_input(microbatch) gives rank 0 its input for token step 0.
     """
 
-    def __init__(self, rank: int, world: int, stage_fn, first_input, total_steps: int, group=None, dist=None):
+    def __init__(self, rank: int, world: int, stage_fn, first_input, total_steps: int, group=None, dist=None,
+                 recv_spec=None):
+        # recv_spec(unit) -> (shape, dtype, device) of the tensor this rank consumes as input of `unit`;
+        # None: same shape as what it sends
+        self.recv_spec = recv_spec
         self.rank, self.world = rank, world
         self.stage_fn, self.first_input = stage_fn, first_input
         self.units = total_steps * world
@@ -139,8 +143,12 @@ class RingPipeline:
                 if send:
                     p2p.append(self.dist.P2POp(self.dist.isend, y, nxt, self.group))
                 if recv:
-                    like = y if y is not None else (self.inbox if self.inbox is not None else self.first_input(0))
-                    buf = torch.empty_like(like)
+                    if self.recv_spec is not None:
+                        shape, dtype, device = self.recv_spec(t + 1 - r)
+                        buf = torch.empty(shape, dtype=dtype, device=device)
+                    else:
+                        like = y if y is not None else (self.inbox if self.inbox is not None else self.first_input(0))
+                        buf = torch.empty_like(like)
                     p2p.append(self.dist.P2POp(self.dist.irecv, buf, prv, self.group))
                 if p2p:
                     for req in self.dist.batch_isend_irecv(p2p):
