@@ -10,7 +10,8 @@ from .kvcache import (ChunkHandle, ChunkPool, CopiedPinnedMemory, CpuChunkPool, 
                       KVCacheManager, PagedKVCache, PagePool, PageTableAllocator, PageTableHandle, PinnedMemory,
                       VirtualPagedKVCache, VirtualPagePool)
 from .ops import (BatchDecodeWithPagedKVCacheWrapper, BatchPrefillWithPagedKVCacheWrapper, append_paged_kv_cache,
-                  apply_rope, apply_rope_inplace, paged_decode, paged_prefill)
+                  apply_rope, apply_rope_inplace, greedy_sample, paged_decode, paged_prefill, rmsnorm,
+                  rope_append_paged_kv_cache)
 from .engine import (BatchDecode, BatchPrefill, BatchResult, KVStage, MicroBatchProcessor, RingPipeline, StageProcessor,
                      StepRequest)
 from .model import LlamaStage, ModelArgs

@@ -57,8 +57,7 @@ def init_weight(shape, seed: int, device, dtype, std: float = 0.02) -> torch.Ten
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+    return ops.rmsnorm(x, weight, eps)
 
 
 class LlamaStage:
@@ -99,10 +98,9 @@ class LlamaStage:
         q = qkv[:, :nq].unflatten(1, (a.n_heads, hd))
         k = qkv[:, nq : nq + nkv].unflatten(1, (a.n_kv_heads, hd))
         v = qkv[:, nq + nkv :].unflatten(1, (a.n_kv_heads, hd))
-        ops.apply_rope_inplace(q, k, ctx.indptr, ctx.offsets, True, a.rope_theta)
         pages = ctx.page_pool.get_layered_pages(ctx.layer_id)
-        ops.append_paged_kv_cache(k, v, ctx.indptr, pages, ctx.kv_page_indices, ctx.kv_page_indptr,
-                                  ctx.kv_last_page_lens)
+        ops.rope_append_paged_kv_cache(q, k, v, ctx.indptr, ctx.offsets, pages, ctx.kv_page_indices,
+                                       ctx.kv_page_indptr, ctx.kv_last_page_lens, a.rope_theta)
         if isinstance(ctx, FlashDecodeCtx):
             attn = ctx.decode_wrapper.forward(q, pages)
         else:
@@ -134,7 +132,7 @@ class LlamaStage:
         argmax and one device->host copy instead of the reference's per-task
         argmax + cat, layer_storage.py:219-253). Returns (tokens [bsz] int32 on the
         device, mask of requests that produced a token, ids done)."""
-        tokens = torch.argmax(logits.float(), dim=-1).to(torch.int32)
+        tokens = ops.greedy_sample(logits)
         produced, done = [], []
         for t in task_datas:
             fin = t.finished_prefill()

@@ -307,3 +307,49 @@ class BatchPrefillWithPagedKVCacheWrapper:
 
     def end_forward(self) -> None:
         self._desc = None
+
+
+def rope_append_paged_kv_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, indptr: torch.Tensor,
+                               offsets: torch.Tensor, paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor,
+                               kv_indptr: torch.Tensor, kv_last_page_len: torch.Tensor,
+                               rope_theta: float = 500000.0) -> None:
+    """apply_rope + append_paged_kv_cache in one launch: q rotated in place, rotated
+    k and plain v written into their page slots."""
+    _lib.require_cuda(q, k, v, paged_kv_cache)
+    ps, hkv, d, page_stride = _pages_view(paged_kv_cache)
+    if not (q.dtype == k.dtype == v.dtype == paged_kv_cache.dtype):
+        raise ValueError("rope_append: dtypes of q, k, v and the pages differ")
+    hq = q.shape[1]
+    qs, ks, vs = _row_stride(q, hq, d, "q"), _row_stride(k, hkv, d, "k"), _row_stride(v, hkv, d, "v")
+    _lib.check(_lib.lib.dsv_rope_append_paged_kv(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), qs, ks, vs, _i32_dev(indptr, "indptr").data_ptr(),
+        _i32_dev(offsets, "offsets").data_ptr(), paged_kv_cache.data_ptr(), page_stride, paged_kv_cache.shape[0],
+        _i32_dev(kv_indices, "kv_indices").data_ptr(), _i32_dev(kv_indptr, "kv_indptr").data_ptr(),
+        _i32_dev(kv_last_page_len, "kv_last_page_len").data_ptr(), kv_last_page_len.shape[0], q.shape[0], hq, hkv, d, ps,
+        float(rope_theta), rope_inv_freq(d, rope_theta).data_ptr(), _lib.dtype_code(q.dtype),
+        _lib.current_stream_ptr(q.device)))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x * rsqrt(mean(x^2) + eps) * weight over the last dimension of a [rows, dim] tensor."""
+    _lib.require_cuda(x, weight)
+    if x.dim() != 2 or x.stride(1) != 1 or weight.shape != (x.shape[1],) or weight.dtype != x.dtype:
+        raise ValueError("rmsnorm: x must be [rows, dim] with dense rows and weight [dim] of the same dtype")
+    if out is None:
+        out = torch.empty_like(x, memory_format=torch.contiguous_format)
+    _lib.check(_lib.lib.dsv_rmsnorm(x.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr(), x.stride(0),
+                                    out.stride(0), x.shape[0], x.shape[1], float(eps), _lib.dtype_code(x.dtype),
+                                    _lib.current_stream_ptr(x.device)))
+    return out
+
+
+def greedy_sample(logits: torch.Tensor) -> torch.Tensor:
+    """int32 argmax of every row of [rows, vocab] logits (lowest index among ties)."""
+    _lib.require_cuda(logits)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("greedy_sample: logits must be [rows, vocab] with dense rows")
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib.dsv_greedy_sample(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1],
+                                          out.data_ptr(), _lib.dtype_code(logits.dtype),
+                                          _lib.current_stream_ptr(logits.device)))
+    return out

@@ -97,6 +97,40 @@ int dsv_apply_rope_inplace(void* q, void* k, int64_t q_stride_tok, int64_t k_str
                            const float* inv_freq_host, int dtype, void* stream);
 
 /*
+ * Rotary embedding fused into the append-scatter: q is rotated in place, k is
+ * rotated and written straight into its page slot, v is copied into its page
+ * slot (k itself is left untouched). One launch instead of the reference's
+ * apply_rope + append_paged_kv_cache pair (deserve_worker/model/layer/
+ * attention.py:166-183); the rotation is the same fp32 expression as
+ * dsv_apply_rope_inplace, so pages and q agree with that pair bit for bit.
+ */
+int dsv_rope_append_paged_kv(void* q, const void* k, const void* v, int64_t q_stride_tok,
+                             int64_t k_stride_tok, int64_t v_stride_tok,
+                             const int32_t* qo_indptr, const int32_t* offsets, void* pages_layer,
+                             int64_t page_stride, int64_t num_pages, const int32_t* kv_indices,
+                             const int32_t* kv_indptr, const int32_t* kv_last_page_len, int batch,
+                             int nnz, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                             float rope_theta, const float* inv_freq_host, int dtype,
+                             void* stream);
+
+/*
+ * out[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * weight, fp32 math, rounded
+ * once. Replaces flashinfer.norm.rmsnorm(x, weight, eps) at
+ * deserve_worker/model/layer/norm.py:34 (torch statement: norm.py:18-19, 37-39).
+ * Row strides in elements; out may alias x.
+ */
+int dsv_rmsnorm(const void* x, const void* weight, void* out, int64_t x_stride,
+                int64_t out_stride, int rows, int dim, float eps, int dtype, void* stream);
+
+/*
+ * Greedy sampling: tokens[r] = argmax of logits[r, 0..vocab), the lowest index
+ * among equal maxima. Replaces the per-task torch.argmax + torch.cat loop of
+ * deserve_worker/layer_storage.py:219-253 (temperature 0 branch, line 250).
+ */
+int dsv_greedy_sample(const void* logits, int64_t row_stride, int rows, int vocab,
+                      int32_t* tokens, int dtype, void* stream);
+
+/*
  * Host-side planning of the split-KV schedule for paged decode attention.
  * Replaces BatchDecodeWithPagedKVCacheWrapper.begin_forward(...) at
  * deserve_worker/execution/exec.py:184-192. Pure host arithmetic: reads

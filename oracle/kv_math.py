@@ -101,3 +101,16 @@ def token_positions(desc) -> torch.Tensor:
         n = int(desc["indptr"][i + 1] - desc["indptr"][i])
         pos.extend(int(desc["offsets"][i]) + j for j in range(n))
     return torch.tensor(pos, dtype=torch.int64)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """deserve_worker/model/layer/norm.py:18-19 (x * rsqrt(mean(x^2) + eps)) times the
+    weight, evaluated in fp32 and rounded once to x's type, which is what the fused
+    call at norm.py:34 computes."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+def greedy_tokens(logits: torch.Tensor) -> torch.Tensor:
+    """deserve_worker/layer_storage.py:250: argmax of each row (first maximum)."""
+    return torch.argmax(logits.float(), dim=-1).to(torch.int32)
