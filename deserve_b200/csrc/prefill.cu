@@ -1,23 +1,26 @@
 // Ragged causal attention of new q rows against paged K/V (chunked prefill and
 // mixed prefill+decode batches) on the 5th-generation tensor cores.
 //
-// One CTA owns one work item: (request, kv head, tile of 128/G q tokens), G =
+// One CTA owns one work item: (request, kv head, two tiles of 128/G q tokens), G =
 // n_q_heads / n_kv_heads. The G q heads of the kv head are stacked with the
-// tokens into the 128 rows of the MMA (row = token * G + head), so a K/V tile is
-// loaded once for the whole GQA group. Per 128-token K/V tile:
+// tokens into the 128 rows of an MMA (row = token * G + head), so a K/V tile is
+// loaded once for the whole GQA group and for both q tiles. Per 128-token K/V
+// tile and per q tile:
 //     S = Q K^T      tcgen05.mma (kind::f16, M=128, N=128, K=16 x D/16), A and B from
-//                    128B-swizzled shared memory, accumulator in TMEM (double buffered)
-//     softmax        warps 0-3, one thread per row: tcgen05.ld of the row, causal / length
-//                    mask, running maximum with lazy rescaling (O is only rescaled when a
-//                    row maximum grew by more than 2^8), P = exp2(...) packed to 16 bit and
-//                    written back to TMEM with tcgen05.st
+//                    128B-swizzled shared memory, accumulator in TMEM
+//     softmax        one warp group per q tile, one thread per row: tcgen05.ld of the row,
+//                    causal / length mask, running maximum with lazy rescaling (O is only
+//                    rescaled when a row maximum grew by more than 2^8), P = 2^(...) packed to
+//                    16 bit and written over S in TMEM with tcgen05.st
 //     O += P V       tcgen05.mma with A = P from TMEM and B = the V tile read MN-major
 //                    (tokens are the K dimension), accumulator O in TMEM
-// Warp 4 is the TMA producer (q tile once; K and V tiles through two 2-stage rings,
-// one cp.async.bulk.tensor per 16-token box and 64-element half of head_dim),
-// warp 5 issues the MMAs from one thread and signals completion with
-// tcgen05.commit on mbarriers. Every wait is bounded; on expiry the kernel records
-// ST_WAIT_TIMEOUT, leaves the loops, frees its TMEM and returns.
+// The two q tiles ping-pong: while one tile's warp group does its softmax, the tensor
+// core runs the other tile's P V and next Q K^T. Warp 8 is the TMA producer of q and
+// the K ring, warp 10 of the V ring (2 stages each, one cp.async.bulk.tensor per
+// 16-token box and 64-element half of head_dim), warp 9 issues the MMAs from one
+// thread and signals completion with tcgen05.commit on mbarriers. Every wait is
+// bounded; on expiry the kernel records ST_WAIT_TIMEOUT, leaves the loops, frees its
+// TMEM and returns.
 #include <cuda.h>
 
 #include <algorithm>
@@ -30,7 +33,7 @@ namespace dsv {
 namespace {
 
 constexpr int kBN = 128;                 // kv tokens per tile
-constexpr int kThreads = 224;            // 4 softmax warps, K producer, MMA warp, V producer
+constexpr int kThreads = 352;            // 2 x 4 softmax warps, K producer, MMA warp, V producer
 constexpr int kSpinLimit = 1 << 21;
 constexpr int32_t kPrefillMagic = 0x44535032;  // "DSP2"
 constexpr int kPlanHeader = 8;
@@ -186,36 +189,38 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
+// Warp roles: 0-3 softmax of q tile A, 4-7 softmax of q tile B (thread = row = TMEM lane), 8 TMA
+// producer of q and the K ring, 9 MMA issuer, 10 TMA producer of the V ring.
+// TMEM columns: tile X owns [256 X, 256 X + 256): S at +0 (P is written over its first 64 columns
+// once the row has been read), O at +128.
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                const PrefillParams p) {
   constexpr int DH = D / 64;
-  constexpr int QTILE = 128 * D * 2;      // q tile bytes: [DH][128 rows][128 B]
+  constexpr int QTILE = 128 * D * 2;      // one q tile: [DH][128 rows][128 B]
   constexpr int KVTILE = kBN * D * 2;     // one K (or V) stage: [DH][128 tokens][128 B]
   constexpr int HALF_ROWS = 128 * 128;    // bytes of one 64-element half: 128 rows x 128 B
-  constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
   constexpr uint32_t IDESC_QK = instr_desc(kBf16 ? 1 : 0, 0, kBN, 128);
   constexpr uint32_t IDESC_PV = instr_desc(kBf16 ? 1 : 0, 1, D, 128);
-  // TMEM columns
-  constexpr uint32_t COL_S0 = 0, COL_S1 = 384, COL_P = 128, COL_O = 256;
+  constexpr uint32_t COL_S = 0, COL_O = 128, COL_TILE = 256;
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_smem = base;
-  const uint32_t k_smem = q_smem + QTILE;             // 2 stages
+  const uint32_t q_smem = base;                       // 2 q tiles
+  const uint32_t k_smem = q_smem + 2 * QTILE;         // 2 stages
   const uint32_t v_smem = k_smem + 2 * KVTILE;        // 2 stages
   const uint32_t bars = v_smem + 2 * KVTILE;
-  // barrier slots (8 bytes each)
+  // barrier slots (8 bytes each): q, kfull[2], vfull[2], kempty[2], vempty[2], sfull[2 tiles], pfull[2], odone[2]
   const uint32_t bar_q = bars, bar_kfull = bars + 8, bar_vfull = bars + 24, bar_kempty = bars + 40,
-                 bar_vempty = bars + 56, bar_sfull = bars + 72, bar_pfull = bars + 88, bar_odone = bars + 96;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 104);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bars - base) + 108);
+                 bar_vempty = bars + 56, bar_sfull = bars + 72, bar_pfull = bars + 88, bar_odone = bars + 104;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 120);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.n_q_heads / p.n_kv_heads;
-  const int tq = 128 / G;
+  const int tq = 128 / G;                  // q tokens per tile
   const int kv_head = blockIdx.y;
   const int ps_log = p.ps_log2, ps = 1 << ps_log;
   const int bt = min(ps, 16), n_boxes = kBN / bt;
@@ -227,7 +232,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   const int ip0 = __ldg(p.kv_indptr + req), ip1 = __ldg(p.kv_indptr + req + 1);
   const int kv_len = ip1 > ip0 ? (ip1 - ip0 - 1) * ps + __ldg(p.kv_last_page_len + req) : 0;
   const int n_tiles = (kv_hi + kBN - 1) / kBN;
-  const bool bad = q0 < 0 || nq < 1 || nq > tq || q0 + nq > n_new || kv_hi < 1 || kv_hi > kv_len;
+  const bool has_b = nq > tq;              // the second q tile holds live rows
+  const bool bad = q0 < 0 || nq < 1 || nq > 2 * tq || q0 + nq > n_new || kv_hi < 1 || kv_hi > kv_len;
   if (bad) {
     if (tid == 0) record_status(p.status, ST_BAD_PLAN);
     return;
@@ -241,13 +247,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       mbar_init(bar_kempty + 8 * s, 1);
       mbar_init(bar_vempty + 8 * s, 1);
       mbar_init(bar_sfull + 8 * s, 1);
+      mbar_init(bar_pfull + 8 * s, 128);
+      mbar_init(bar_odone + 8 * s, 1);
     }
-    mbar_init(bar_pfull, 128);
-    mbar_init(bar_odone, 1);
-    *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 4) {  // TMEM: all 512 columns (one CTA per SM)
+  if (warp == 8) {  // TMEM: all 512 columns (one CTA per SM)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
                      smem_u32(const_cast<uint32_t*>(tmem_slot))),
                  "r"(512)
@@ -259,211 +264,217 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4 || warp == 6) {
-    // ================================ TMA producers: warp 4 = q + K ring, warp 6 = V ring =============================================
-    if (warp == 4 && lane == 0) {
-      mbar_expect_tx(bar_q, QTILE);
-      for (int dh = 0; dh < DH; ++dh)
-        tma_load_4d(q_smem + dh * HALF_ROWS, &q_map, bar_q, 0, kv_head * G, dh, q_begin + q0);
+  if (warp == 8 || warp == 10) {
+    // ================================ TMA producers: warp 8 = q + K ring, warp 10 = V ring =======
+    if (warp == 8 && lane == 0) {
+      mbar_expect_tx(bar_q, (uint32_t)(QTILE * (has_b ? 2 : 1)));
+      for (int x = 0; x < (has_b ? 2 : 1); ++x)
+        for (int dh = 0; dh < DH; ++dh)
+          tma_load_4d(q_smem + x * QTILE + dh * HALF_ROWS, &q_map, bar_q, 0, kv_head * G, dh, q_begin + q0 + x * tq);
     }
     const int32_t* idx = p.kv_indices + ip0;
-    bool failed = false;
+    const int kv = warp == 10 ? 1 : 0;
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int s = tile & 1;
       const int t0 = tile * kBN;
       int live = 0;  // boxes that hold at least one visible token
       for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
-      // K and V rings advance independently: the K stage is free as soon as Q K^T of two tiles
-      // ago has run (long before that tile's P V), so the next K tile is always in flight early
-      // and the MMA warp never waits for it.
-      {
-        const int kv = warp == 6 ? 1 : 0;
-        const uint32_t full = (kv ? bar_vfull : bar_kfull) + 8 * s, empty = (kv ? bar_vempty : bar_kempty) + 8 * s;
-        if (tile >= 2 && !warp_wait(empty, ((tile >> 1) - 1) & 1, p.status)) {
-          *abort_flag = 1;
-          failed = true;
-          break;
+      // The K and V rings advance on their own barriers and in their own warps: a K stage is free
+      // as soon as Q K^T of two tiles ago has run, so the next K tile is in flight long before the
+      // MMA warp asks for it, whatever the V ring is waiting for.
+      const uint32_t full = (kv ? bar_vfull : bar_kfull) + 8 * s, empty = (kv ? bar_vempty : bar_kempty) + 8 * s;
+      if (tile >= 2 && !warp_wait(empty, ((tile >> 1) - 1) & 1, p.status)) break;
+      if (lane == 0) mbar_expect_tx(full, (uint32_t)(live * DH * bt * 128));
+      __syncwarp();
+      for (int b = lane; b < n_boxes; b += 32) {
+        const int tok = t0 + b * bt;
+        if (tok >= kv_hi) continue;
+        int page = __ldg(idx + (tok >> ps_log));
+        if (page < 0 || page >= p.num_pages) {
+          record_status(p.status, ST_BAD_PAGE_ID);
+          page = 0;
         }
-        if (lane == 0) mbar_expect_tx(full, (uint32_t)(live * DH * bt * 128));
-        __syncwarp();
-        for (int b = lane; b < n_boxes; b += 32) {
-          const int tok = t0 + b * bt;
-          if (tok >= kv_hi) continue;
-          int page = __ldg(idx + (tok >> ps_log));
-          if (page < 0 || page >= p.num_pages) {
-            record_status(p.status, ST_BAD_PAGE_ID);
-            page = 0;
-          }
-          const int in_page = tok & (ps - 1);
-          for (int dh = 0; dh < DH; ++dh) {
-            const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
-            tma_load_5d((kv ? v_smem : k_smem) + off, &kv_map, full, 0, in_page, kv_head, dh, 2 * page + kv);
-          }
+        const int in_page = tok & (ps - 1);
+        for (int dh = 0; dh < DH; ++dh) {
+          const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
+          tma_load_5d((kv ? v_smem : k_smem) + off, &kv_map, full, 0, in_page, kv_head, dh, 2 * page + kv);
         }
       }
-      if (failed) break;
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ================================ MMA issuer (one thread) ===================================
+    // Issue order per K/V tile j: P_A V, next Q_A K^T, P_B V, next Q_B K^T. While the softmax warps
+    // of one q tile work, the tensor core runs the other tile's two products.
     if (lane == 0) {
       bool ok = mbar_wait(bar_q, 0, p.status);
-      auto issue_qk = [&](int tile) {  // S[tile & 1] = Q K_tile^T
+      auto issue_qk = [&](int tile, int x) {  // S_x = Q_x K_tile^T
         const int s = tile & 1;
-        const uint32_t d = tmem + (s ? COL_S1 : COL_S0);
+        const uint32_t d = tmem + x * COL_TILE + COL_S;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t koff = (uint32_t)((kk >> 2) * HALF_ROWS + (kk & 3) * 32);
-          umma_ss(d, smem_desc(q_smem + koff, 16, 1024), smem_desc(k_smem + s * KVTILE + koff, 16, 1024), IDESC_QK,
-                  kk > 0 ? 1u : 0u);
+          umma_ss(d, smem_desc(q_smem + x * QTILE + koff, 16, 1024), smem_desc(k_smem + s * KVTILE + koff, 16, 1024),
+                  IDESC_QK, kk > 0 ? 1u : 0u);
         }
-        tc_commit(bar_sfull + 8 * s);
-        tc_commit(bar_kempty + 8 * s);
+        tc_commit(bar_sfull + 8 * x);
+        if (x == (has_b ? 1 : 0)) tc_commit(bar_kempty + 8 * s);  // last reader of this K stage
+      };
+      auto issue_pv = [&](int tile, int x) {  // O_x += P_x V_tile
+        const int s = tile & 1;
+        const int cols = min(kBN, kv_hi - tile * kBN);
+        const int ksteps = (cols + 15) >> 4;  // 16-token steps that hold a visible token
+        for (int kt = 0; kt < ksteps; ++kt)
+          umma_ts(tmem + x * COL_TILE + COL_O, tmem + x * COL_TILE + COL_S + kt * 8,
+                  smem_desc(v_smem + s * KVTILE + kt * 2048, HALF_ROWS, 1024), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
+        tc_commit(bar_odone + 8 * x);
+        if (x == (has_b ? 1 : 0)) tc_commit(bar_vempty + 8 * s);  // last reader of this V stage
       };
       if (ok) ok = mbar_wait(bar_kfull, 0, p.status);
       if (ok) {
         tc_fence_after();
-        issue_qk(0);
+        issue_qk(0, 0);
+        if (has_b) issue_qk(0, 1);
       }
       for (int tile = 0; ok && tile < n_tiles; ++tile) {
         const int s = tile & 1;
-        if (tile + 1 < n_tiles) {  // next S while the softmax warps work on this one
-          ok = mbar_wait(bar_kfull + 8 * (s ^ 1), ((tile + 1) >> 1) & 1, p.status);
+        const bool more = tile + 1 < n_tiles;
+        for (int x = 0; ok && x < (has_b ? 2 : 1); ++x) {
+          ok = mbar_wait(bar_pfull + 8 * x, tile & 1, p.status);
+          if (ok && x == 0) ok = mbar_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status);
           if (!ok) break;
           tc_fence_after();
-          issue_qk(tile + 1);
+          issue_pv(tile, x);
+          if (more) {
+            if (x == 0) ok = mbar_wait(bar_kfull + 8 * (s ^ 1), ((tile + 1) >> 1) & 1, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(tile + 1, x);  // runs after P_x V (in issue order), so S_x / P_x may be overwritten
+          }
         }
-        ok = mbar_wait(bar_pfull, tile & 1, p.status) && mbar_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status);
-        if (!ok) break;
-        tc_fence_after();
-        const int cols = min(kBN, kv_hi - tile * kBN);
-        const int ksteps = (cols + 15) >> 4;  // 16-token steps that hold a visible token
-        for (int kt = 0; kt < ksteps; ++kt)
-          umma_ts(tmem + COL_O, tmem + COL_P + kt * 8,
-                  smem_desc(v_smem + s * KVTILE + kt * 2048, HALF_ROWS, 1024), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
-        tc_commit(bar_odone);
-        tc_commit(bar_vempty + 8 * s);
       }
-      if (!ok) *abort_flag = 1;
     }
   } else {
     // ================================ softmax / correction / epilogue ============================
-    const int row = tid;                      // TMEM lane and MMA row
-    const int tok_local = row / G, head = row - tok_local * G;
-    const bool row_live = tok_local < nq;
-    // last kv position this row may see
-    const int limit = min(p.causal ? (kv_len - n_new + q0 + tok_local) : (kv_len - 1), kv_hi - 1);
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const float sc = p.scale_log2;
-    float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int tile = 0; tile < n_tiles; ++tile) {
-      const int s = tile & 1;
-      if (!warp_wait(bar_sfull + 8 * s, (tile >> 1) & 1, p.status)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t s_addr = tmem + lane_base + (s ? COL_S1 : COL_S0);
-      const int t0 = tile * kBN;
-      const bool need_mask = (t0 + kBN - 1) > limit;
-      // the whole S row in registers: four 32-column loads in flight, one wait
-      uint32_t r[kBN];
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-      tmem_wait_ld();
-      float mx = -INFINITY;
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < kBN; ++i)
-          if (t0 + i > limit) r[i] = 0xff800000u;  // -inf
-      }
-#pragma unroll
-      for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-      const float m_tile = mx * sc;
-      // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 2^8
-      float factor = 1.f;
-      if (m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY)) {
-        factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_tile);
-        m_used = m_tile;
-      }
-      if (tile > 0) {  // O and P are free once the previous P.V has completed
-        if (!warp_wait(bar_odone, (tile - 1) & 1, p.status)) { ok = false; break; }
+    const int x = warp >> 2;                  // q tile of this warp group
+    const int row = tid & 127;                // TMEM lane and MMA row
+    if (x == 0 || has_b) {
+      const int tok_local = x * tq + row / G, head = row % G;
+      const bool row_live = tok_local < nq;
+      // last kv position this row may see
+      const int limit = min(p.causal ? (kv_len - n_new + q0 + tok_local) : (kv_len - 1), kv_hi - 1);
+      const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+      const uint32_t s_addr = tmem + lane_base + x * COL_TILE + COL_S;
+      const uint32_t o_addr = tmem + lane_base + x * COL_TILE + COL_O;
+      const float sc = p.scale_log2;
+      float m_used = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        const int s = tile & 1;
+        if (!warp_wait(bar_sfull + 8 * x, tile & 1, p.status)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, factor != 1.f)) {
-          l *= factor;
-#pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tmem + lane_base + COL_O + c * 32, o);
-            tmem_wait_ld();
+        const int t0 = tile * kBN;
+        const bool need_mask = (t0 + kBN - 1) > limit;
+        // the whole S row in registers: four 32-column loads in flight, one wait
+        uint32_t r[kBN];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-            tmem_st32(tmem + lane_base + COL_O + c * 32, o);
-          }
-        }
-      }
-      // P = exp2(S * scale - m_used) (masked entries are exp2(-inf) = 0), written to TMEM as 16-bit pairs
-      const float off = (m_used == -INFINITY) ? 0.f : m_used;
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i]), sc, -off));
-          const float b = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i + 1]), sc, -off));
-          l0 += a;
-          l1 += b;
-          pk[i] = pack2<T>(a, b);
-        }
-        tmem_st16(tmem + lane_base + COL_P + c * 16, pk);
-      }
-      l += l0 + l1;
-      tmem_wait_st();
-      // Rows of V past the visible length hold whatever the pool (or an older tile) left there;
-      // clear the ones inside the last issued 16-token step so that 0 * garbage stays 0.
-      const int cols = min(kBN, kv_hi - t0);
-      if (cols < kBN && (cols & 15) != 0) {
-        if (!warp_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status)) { ok = false; break; }
-        const int r0 = cols, r1 = (cols + 15) & ~15;
-        for (int x = tid; x < (r1 - r0) * DH * 8; x += 128) {
-          const int ch = x & 7, dh = (x >> 3) % DH, rr = r0 + (x >> 3) / DH;
-          *reinterpret_cast<uint4*>(smem + (v_smem - base) + s * KVTILE + dh * HALF_ROWS + rr * 128 + ch * 16) =
-              make_uint4(0, 0, 0, 0);
-        }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      }
-      tc_fence_before();
-      mbar_arrive(bar_pfull);
-    }
-    if (ok) ok = warp_wait(bar_odone, (n_tiles - 1) & 1, p.status);
-    if (ok) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      T* dst = reinterpret_cast<T*>(p.out) + (int64_t)(q_begin + q0 + tok_local) * p.out_stride +
-               (int64_t)(kv_head * G + head) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + COL_O + c * 32, r);
+        for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
         tmem_wait_ld();
-        if (row_live) {
+        float mx = -INFINITY;
+        if (need_mask) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t w[4];
+          for (int i = 0; i < kBN; ++i)
+            if (t0 + i > limit) r[i] = 0xff800000u;  // -inf
+        }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              w[i] = pack2<T>(__uint_as_float(r[v * 8 + 2 * i]) * inv, __uint_as_float(r[v * 8 + 2 * i + 1]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        const float m_tile = mx * sc;
+        // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 2^8
+        float factor = 1.f;
+        if (m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY)) {
+          factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_tile);
+          m_used = m_tile;
+        }
+        if (tile > 0) {  // O is free once the previous P.V has completed
+          if (!warp_wait(bar_odone + 8 * x, (tile - 1) & 1, p.status)) { ok = false; break; }
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, factor != 1.f)) {
+            l *= factor;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(o_addr + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_st32(o_addr + c * 32, o);
+            }
+          }
+        }
+        // P = 2^(S * scale - m_used) (masked entries give 2^-inf = 0), written over S as 16-bit pairs
+        const float off = (m_used == -INFINITY) ? 0.f : m_used;
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i]), sc, -off));
+            const float b = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i + 1]), sc, -off));
+            l0 += a;
+            l1 += b;
+            pk[i] = pack2<T>(a, b);
+          }
+          tmem_st16(s_addr + c * 16, pk);
+        }
+        l += l0 + l1;
+        tmem_wait_st();
+        // Rows of V past the visible length hold whatever the pool (or an older tile) left there;
+        // clear the ones inside the last issued 16-token step so that 0 * garbage stays 0. Both
+        // warp groups write the same zeros; each does it before releasing its own P.
+        const int cols = min(kBN, kv_hi - t0);
+        if (cols < kBN && (cols & 15) != 0) {
+          if (!warp_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status)) { ok = false; break; }
+          const int r0 = cols, r1 = (cols + 15) & ~15;
+          for (int z = row; z < (r1 - r0) * DH * 8; z += 128) {
+            const int ch = z & 7, dh = (z >> 3) % DH, rr = r0 + (z >> 3) / DH;
+            *reinterpret_cast<uint4*>(smem + (v_smem - base) + s * KVTILE + dh * HALF_ROWS + rr * 128 + ch * 16) =
+                make_uint4(0, 0, 0, 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
+        tc_fence_before();
+        mbar_arrive(bar_pfull + 8 * x);
+      }
+      if (ok) ok = warp_wait(bar_odone + 8 * x, (n_tiles - 1) & 1, p.status);
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* dst = reinterpret_cast<T*>(p.out) + (int64_t)(q_begin + q0 + tok_local) * p.out_stride +
+                 (int64_t)(kv_head * G + head) * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_wait_ld();
+          if (row_live) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                w[i] = pack2<T>(__uint_as_float(o[v * 8 + 2 * i]) * inv, __uint_as_float(o[v * 8 + 2 * i + 1]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
           }
         }
       }
-    } else {
-      *abort_flag = 1;
     }
   }
 
   // ---- teardown: everyone meets here, then the allocating warp frees TMEM ----------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
   }
@@ -514,8 +525,8 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
     const int n = qo_indptr_host[i + 1] - qo_indptr_host[i];
     const int len = kv_len_host[i];
     DSV_REQUIRE(n >= 0 && len >= n, "prefill_plan: request %d has %d new tokens but kv length %d", i, n, len);
-    for (int q0 = 0; q0 < n; q0 += tq) {
-      const int nq = std::min(tq, n - q0);
+    for (int q0 = 0; q0 < n; q0 += 2 * tq) {  // a work item is two q tiles of the same request
+      const int nq = std::min(2 * tq, n - q0);
       const int hi = causal ? len - n + q0 + nq : len;  // kv positions the tile's last token sees
       items.push_back({i, q0, nq, hi});
     }
@@ -604,7 +615,7 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
   p.out_stride = out_stride_tok; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.ps_log2 = ps_log2;
   p.num_pages = (int)num_pages; p.causal = causal ? 1 : 0; p.scale_log2 = sm_scale * kLog2e;
   p.status = device_status_ptr();
-  const size_t smem = (size_t)128 * head_dim * 2 + 4 * (size_t)kBN * head_dim * 2 + 128 + 1024;
+  const size_t smem = (size_t)2 * 128 * head_dim * 2 + 4 * (size_t)kBN * head_dim * 2 + 128 + 1024;
   const dim3 grid((unsigned)n_items, (unsigned)n_kv_heads);
   auto go = [&](auto kernel) -> cudaError_t {
     cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

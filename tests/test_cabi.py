@@ -113,7 +113,7 @@ def test_prefill_plan_tiles_every_new_token_once(causal):
     items = plan[8:used].reshape(-1, 4)
     cover = [np.zeros(n, dtype=int) for n in np.diff(qo)]
     for req, q0, nq, hi in items:
-        assert 1 <= nq <= tq and q0 % tq == 0
+        assert 1 <= nq <= 2 * tq and q0 % (2 * tq) == 0  # an item is two q tiles
         cover[req][q0 : q0 + nq] += 1
         n = qo[req + 1] - qo[req]
         assert hi == (kv_len[req] - n + q0 + nq if causal else kv_len[req])
