@@ -385,8 +385,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           for (int i = 0; i < kBN; ++i)
             if (t0 + i > limit) r[i] = 0xff800000u;  // -inf
         }
+        {  // eight independent chains instead of one 128-long dependent one
+          float m8[8];
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(r[i]);
+#pragma unroll
+          for (int i = 8; i < kBN; ++i) m8[i & 7] = fmaxf(m8[i & 7], __uint_as_float(r[i]));
+          mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        }
         const float m_tile = mx * sc;
         // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 2^8
         float factor = 1.f;
@@ -412,7 +418,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         }
         // P = 2^(S * scale - m_used) (masked entries give 2^-inf = 0), written over S as 16-bit pairs
         const float off = (m_used == -INFINITY) ? 0.f : m_used;
-        float l0 = 0.f, l1 = 0.f;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < kBN / 32; ++c) {
           uint32_t pk[16];
@@ -420,13 +426,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           for (int i = 0; i < 16; ++i) {
             const float a = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i]), sc, -off));
             const float b = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i + 1]), sc, -off));
-            l0 += a;
-            l1 += b;
+            ls[(2 * i) & 3] += a;
+            ls[(2 * i + 1) & 3] += b;
             pk[i] = pack2<T>(a, b);
           }
           tmem_st16(s_addr + c * 16, pk);
         }
-        l += l0 + l1;
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         tmem_wait_st();
         // Rows of V past the visible length hold whatever the pool (or an older tile) left there;
         // clear the ones inside the last issued 16-token step so that 0 * garbage stays 0. Both
