@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the paged KV-cache hot path (BASELINE.json configs[1]).
+"""Benchmark of the paged KV-cache hot path (the Llama-3-8B-shaped decode configuration).
 
 Workload "llama3-8b-decode-kv": 32 layers, 32 q / 8 kv heads, head_dim 128,
 bf16, page size 16; 256 sequences with context lengths uniform in [512, 4096];
@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--prefill-reqs", type=int, default=32)
     ap.add_argument("--prefill-ctx", type=int, default=4096)
     ap.add_argument("--prefill-chunk", type=int, default=512)
-    ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (BASELINE config 3)")
+    ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (16 GiB of scattered pages out and back)")
     ap.add_argument("--swap-seqs", type=int, default=64)
     ap.add_argument("--swap-tokens", type=int, default=2048)
     return ap.parse_args()
@@ -235,7 +235,7 @@ def host_link_peak(dev, nbytes=1 << 30, reps=5):
 
 
 def prefill_measure(dk, args, dev, iters=5):
-    """Chunked-prefill attention (BASELINE config 5 shape): prefill_reqs requests that already hold
+    """Chunked-prefill attention (mixed prefill/decode configuration's shape): prefill_reqs requests that already hold
     prefill_ctx tokens each get a chunk of prefill_chunk new tokens; ragged causal attention of the
     chunk against the paged K/V on the tcgen05 kernel, one layer. Reports dense-equivalent TFLOP/s
     (4 * Hq * D * visible (q, kv) pairs) against the measured bf16 GEMM peak."""
@@ -287,7 +287,7 @@ def prefill_measure(dk, args, dev, iters=5):
 
 
 def swap_stress(dk, pool, free_ids, args, dev, decode_step):
-    """BASELINE config 3: the KV of swap_seqs x swap_tokens tokens, all layers, scattered over the
+    """KV swap stress: the KV of swap_seqs x swap_tokens tokens, all layers, scattered over the
     permuted pool, is swapped out to pinned host chunks and back into DIFFERENT pages while decode
     attention of another microbatch runs on the main stream. Bit-exactness is checked with a 32-bit
     checksum of every (layer, page) before and after, and exactly on the first and last layer."""

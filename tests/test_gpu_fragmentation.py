@@ -1,4 +1,4 @@
-"""Mixed prefill / decode under page churn (BASELINE config 5 at test scale): lognormal
+"""Mixed prefill / decode under page churn (the fragmentation configuration at test scale): lognormal
 prompt lengths prefilled in chunks through the tensor-core prefill kernel, decode
 steps through the decode kernel, sequences finishing at seeded random times, their
 pages freed and handed to new arrivals. The product's host classes and the oracle's

@@ -1,7 +1,7 @@
 """Parity of the CUDA path (through the C ABI) with the CPU oracle on the same
 seeded inputs. Data movement is compared bit for bit; attention within the
 stated tolerance of an fp32 reference (2e-2 max-abs for 16-bit types, the bound
-BASELINE's north star gives; 2e-5 for fp32)."""
+the target specification gives; 2e-5 for fp32)."""
 import numpy as np
 import pytest
 import torch
@@ -171,7 +171,7 @@ def test_rope_parity(dtype):
 
 
 def test_config1_decode_loop_bit_exact_pages():
-    """BASELINE config 1: 2 layers, 8 q / 2 kv heads, head_dim 64, fp32, page 16,
+    """The CPU-reference configuration: 2 layers, 8 q / 2 kv heads, head_dim 64, fp32, page 16,
     4 sequences with context U[100,300] from seed 0, 32 decode steps. Page
     contents are compared bit for bit after every step, attention to fp32."""
     L, hq, hkv, d, ps, B, steps = 2, 8, 2, 64, 16, 4, 32
