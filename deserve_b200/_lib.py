@@ -50,6 +50,7 @@ _SIGNATURES = {
     "dsv_last_error": (c_char_p, []),
     "dsv_device_info": (c_int, [POINTER(c_int)] * 3),
     "dsv_read_device_status": (c_int, [POINTER(c_int)]),
+    "dsv_selftest_wait_timeout": (c_int, [c_int, c_void_p]),
     "dsv_append_paged_kv": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "dsv_apply_rope_inplace": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,

@@ -667,4 +667,27 @@ int dsv_paged_decode_static(const void* q, int64_t q_stride_tok, const void* pag
                           dtype, sm_scale, stream);
 }
 
+// ---- self-test of the bounded-wait machinery ---------------------------------------------------
+namespace {
+// One thread waits on an mbarrier phase that nobody will ever complete, with a small poll limit;
+// the wait must give up, record ST_WAIT_TIMEOUT and let the kernel end normally.
+__global__ void wait_timeout_selftest_kernel(int polls, int* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t addr = dsv::smem_u32(&bar);
+  dsv::tma_decode::mbar_init(addr, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  bool done = false;
+  for (int i = 0; i < polls && !done; ++i) done = dsv::tma_decode::mbar_try_wait(addr, 0);
+  if (!done) dsv::record_status(status, dsv::ST_WAIT_TIMEOUT);
+}
+}  // namespace
+
+int dsv_selftest_wait_timeout(int polls, void* stream) {
+  using namespace dsv;
+  DSV_REQUIRE(polls > 0 && polls <= (1 << 20), "selftest: polls must be in [1, 2^20]");
+  wait_timeout_selftest_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(polls, device_status_ptr());
+  DSV_CUDA(cudaGetLastError());
+  return DSV_OK;
+}
+
 }  // extern "C"

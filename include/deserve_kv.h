@@ -303,6 +303,15 @@ int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes
                     const void* host_in, void* stream_out, void* stream_in, void* event);
 
 /*
+ * Self-test of the bounded waits every mbarrier-based kernel here uses: launches
+ * one thread that polls (at most `polls` times) a barrier phase nothing will
+ * ever complete. The wait gives up, the kernel ends normally and
+ * dsv_read_device_status then reports 4 (wait timeout); the context stays
+ * usable. No counterpart in the reference (its kernels are third-party).
+ */
+int dsv_selftest_wait_timeout(int polls, void* stream);
+
+/*
  * Device status word of the kernels' self-checks (page id / slot / token
  * bounds, bounded waits). Synchronises the device. *status = 0 when nothing
  * was recorded; otherwise a DSV_E_DEVICE detail code, cleared by the call.

@@ -222,3 +222,14 @@ def test_config1_decode_loop_bit_exact_pages():
             t.step()
             ot.step()
     assert [t.start_pos for t in tasks] == [n + steps for n in ctx_lens]
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait on a barrier nobody completes runs out of polls, the kernel returns, the status word
+    says so and the device keeps working (no trap, no hang)."""
+    assert _lib.read_device_status() == 0
+    _lib.check(_lib.lib.dsv_selftest_wait_timeout(2000, _lib.current_stream_ptr(DEV)))
+    assert _lib.read_device_status() == 4          # wait timeout, cleared by the read
+    assert _lib.read_device_status() == 0
+    x = torch.arange(8, device=DEV)
+    assert int(x.sum()) == 28                      # the context is still usable
