@@ -122,6 +122,17 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// the same two with the accumulate flag fixed to "add to D": no predicate set-up per instruction
+__device__ __forceinline__ void umma_ss_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile("tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, 1;\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+               "r"(idesc)
+               : "memory");
+}
+__device__ __forceinline__ void umma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  asm volatile("tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 1;\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc),
+               "r"(idesc)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -307,14 +318,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // of one q tile work, the tensor core runs the other tile's two products.
     if (lane == 0) {
       bool ok = mbar_wait(bar_q, 0, p.status);
+      // Matrix descriptors are built once; inside the loops a descriptor is one 64-bit add of a
+      // compile-time offset (the start-address field counts 16-byte units). The issuing thread is a
+      // single lane: every instruction it spends per MMA is on the critical path of the tensor core.
+      const uint64_t qd[2] = {smem_desc(q_smem, 16, 1024), smem_desc(q_smem + QTILE, 16, 1024)};
+      const uint64_t kd[2] = {smem_desc(k_smem, 16, 1024), smem_desc(k_smem + KVTILE, 16, 1024)};
+      const uint64_t vd[2] = {smem_desc(v_smem, HALF_ROWS, 1024), smem_desc(v_smem + KVTILE, HALF_ROWS, 1024)};
       auto issue_qk = [&](int tile, int x) {  // S_x = Q_x K_tile^T
         const int s = tile & 1;
         const uint32_t d = tmem + x * COL_TILE + COL_S;
+        const uint64_t qa = qd[x], kb = kd[s];
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t koff = (uint32_t)((kk >> 2) * HALF_ROWS + (kk & 3) * 32);
-          umma_ss(d, smem_desc(q_smem + x * QTILE + koff, 16, 1024), smem_desc(k_smem + s * KVTILE + koff, 16, 1024),
-                  IDESC_QK, kk > 0 ? 1u : 0u);
+          constexpr int kUnit = 16;  // bytes per descriptor address unit
+          const uint64_t koff = (uint64_t)(((kk >> 2) * HALF_ROWS + (kk & 3) * 32) / kUnit);
+          if (kk == 0) umma_ss(d, qa + koff, kb + koff, IDESC_QK, 0u);
+          else umma_ss_acc(d, qa + koff, kb + koff, IDESC_QK);
         }
         tc_commit(bar_sfull + 8 * x);
         if (x == (has_b ? 1 : 0)) tc_commit(bar_kempty + 8 * s);  // last reader of this K stage
@@ -323,9 +342,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         const int s = tile & 1;
         const int cols = min(kBN, kv_hi - tile * kBN);
         const int ksteps = (cols + 15) >> 4;  // 16-token steps that hold a visible token
-        for (int kt = 0; kt < ksteps; ++kt)
-          umma_ts(tmem + x * COL_TILE + COL_O, tmem + x * COL_TILE + COL_S + kt * 8,
-                  smem_desc(v_smem + s * KVTILE + kt * 2048, HALF_ROWS, 1024), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
+        const uint32_t d = tmem + x * COL_TILE + COL_O, a = tmem + x * COL_TILE + COL_S;
+        const uint64_t vb = vd[s];
+        if (ksteps == kBN / 16 && tile > 0) {  // the common case, fully unrolled
+#pragma unroll
+          for (int kt = 0; kt < kBN / 16; ++kt) umma_ts_acc(d, a + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV);
+        } else {
+          for (int kt = 0; kt < ksteps; ++kt)
+            umma_ts(d, a + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
+        }
         tc_commit(bar_odone + 8 * x);
         if (x == (has_b ? 1 : 0)) tc_commit(bar_vempty + 8 * s);  // last reader of this V stage
       };
