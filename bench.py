@@ -137,7 +137,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU oracle arm (cpu_baseline of our line, and the whole --impl reference run)
 # ---------------------------------------------------------------------------
-def cpu_reference_arm(args, steps, warmup, n_seq=32):
+def cpu_reference_arm(args, steps, warmup, n_seq=128):
     """The reference's torch path restated on the host (oracle/): one layer of
     the workload on the first n_seq sequences per sample — append one token by
     index assignment, gather K/V through the page table, dense fp32 attention.
@@ -145,6 +145,7 @@ def cpu_reference_arm(args, steps, warmup, n_seq=32):
     from oracle import kv_math
 
     torch.set_num_threads(os.cpu_count())
+    n_seq = min(n_seq, args.batch)
     lens = make_lengths(args)[:n_seq] + 1
     ps, hkv, d, hq = args.page_size, args.kv_heads, args.head_dim, args.q_heads
     n_pages = (lens + ps - 1) // ps
@@ -553,7 +554,7 @@ def run_ours(args):
         raise SystemExit(f"device self-check fired: status {status}")
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            result["cpu_baseline"], _ = cpu_reference_arm(args, 3, 1)
+            result["cpu_baseline"], _ = cpu_reference_arm(args, 15, 1)  # ~10 s of host work
         print(json.dumps(result), flush=True)
     if world > 1:
         dist.barrier()
