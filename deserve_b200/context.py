@@ -14,6 +14,7 @@ from typing import Any
 import numpy as np
 import torch
 
+from . import _lib
 from .kvcache import PagedKVCache, PagePool
 from .task import TaskData
 
@@ -31,36 +32,52 @@ class PagedForwardCtx(ForwardCtx):
     offsets: torch.Tensor
 
 
-def _ceil4(n: int) -> int:
-    return (n + 3) & ~3
+_NAMES = ("indptr", "kv_page_indptr", "kv_last_page_lens", "offsets", "seqlens", "kv_page_indices")
+
+
+def build_step(task_datas: list[TaskData], kvcaches: list[PagedKVCache], buf: np.ndarray | None = None):
+    """Grow every cache for this step and write the six descriptor arrays into one
+    packed int32 buffer, in ONE native call (dsv_host_build_step). For a chunked
+    prefill the cache is grown to the whole prompt on the first chunk while the
+    descriptors cover only start_pos + seqlen tokens. Returns (buffer, views)."""
+    bsz = len(task_datas)
+    pool = kvcaches[0].pool
+    alloc = kvcaches[0].page_table.allocator
+    ps = pool.page_size
+    start = np.fromiter((t.start_pos for t in task_datas), dtype=np.int32, count=bsz)
+    seqlen = np.fromiter((t.seqlen for t in task_datas), dtype=np.int32, count=bsz)
+    initial = np.fromiter((t.initial_seqlen for t in task_datas), dtype=np.int32, count=bsz)
+    slot = np.fromiter((kv.page_table.offset for kv in kvcaches), dtype=np.int32, count=bsz)
+    occupied = np.fromiter((kv.page_table.occupied for kv in kvcaches), dtype=np.int32, count=bsz)
+    n_idx = int(((start + seqlen + ps - 1) // ps).sum())
+    cap = 5 * (bsz + 4) + n_idx + 4
+    if buf is None or buf.size < cap:
+        buf = np.empty(cap, dtype=np.int32)
+    offs = np.zeros(7, dtype=np.int64)
+    failed = np.full(2, -1, dtype=np.int32)
+    main = getattr(pool, "num_pages_main", -1)
+    isswap = alloc._isswap_np if main >= 0 else None
+    with pool.mutex:
+        rc = _lib.lib.dsv_host_build_step(
+            pool._bitmap.ctypes.data, pool.num_pages, pool._buf_store.ctypes.data, pool._buf_store.size,
+            pool._buf_win[0:].ctypes.data, pool._buf_win[1:].ctypes.data, pool._avails.ctypes.data, pool.fetch_size, ps,
+            main, alloc._tables_np.ctypes.data, None if isswap is None else isswap.ctypes.data,
+            alloc._tables_np.shape[1], bsz, slot.ctypes.data, occupied.ctypes.data, start.ctypes.data,
+            seqlen.ctypes.data, initial.ctypes.data, buf.ctypes.data, buf.size, offs.ctypes.data,
+            failed[0:].ctypes.data, failed[1:].ctypes.data)
+    for kv, occ in zip(kvcaches, occupied.tolist()):  # also after a failure: earlier requests stay grown
+        kv.page_table.occupied = occ
+    if rc == _lib.E_WORKSPACE and failed[0] >= 0:
+        raise ValueError(f"Not enough pages {int(failed[1])} > {pool.num_avails}")
+    _lib.check(rc)
+    sizes = (bsz + 1, bsz + 1, bsz, bsz, bsz, n_idx)
+    views = {n: buf[int(o) : int(o) + sz] for n, o, sz in zip(_NAMES, offs[:6], sizes)}
+    return buf, int(offs[6]), views
 
 
 def pack_descriptors(task_datas: list[TaskData], kvcaches: list[PagedKVCache]) -> dict[str, np.ndarray]:
-    """Grow every cache for this step and return the descriptor arrays on the
-    host. For a chunked prefill the cache is grown to the whole prompt on the
-    first chunk while the descriptors cover only start_pos + seqlen tokens."""
-    bsz = len(task_datas)
-    n_pages = np.empty(bsz, dtype=np.int32)
-    last = np.empty(bsz, dtype=np.int32)
-    seqlens = np.empty(bsz, dtype=np.int32)
-    offsets = np.empty(bsz, dtype=np.int32)
-    rows = []
-    for i, (task, kv) in enumerate(zip(task_datas, kvcaches)):
-        ps = kv.pool.page_size
-        cur = task.start_pos + task.seqlen
-        kv.extend(max(cur, task.initial_seqlen))
-        n_pages[i] = (cur + ps - 1) // ps
-        last[i] = (cur - 1) % ps + 1
-        seqlens[i] = task.seqlen
-        offsets[i] = task.start_pos
-        rows.append(kv.page_table.allocator._tables_np[kv.page_table.offset, : n_pages[i]])
-    indptr = np.zeros(bsz + 1, dtype=np.int32)
-    np.cumsum(seqlens, out=indptr[1:])
-    kv_page_indptr = np.zeros(bsz + 1, dtype=np.int32)
-    np.cumsum(n_pages, out=kv_page_indptr[1:])
-    kv_page_indices = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int32)
-    return {"indptr": indptr, "kv_page_indptr": kv_page_indptr, "kv_last_page_lens": last, "offsets": offsets,
-            "seqlens": seqlens, "kv_page_indices": kv_page_indices}
+    """The descriptor arrays of a step on the host (caches are grown as a side effect)."""
+    return build_step(task_datas, kvcaches)[2]
 
 
 @dataclass
@@ -73,22 +90,22 @@ class FlashForwardCtx(PagedForwardCtx):
 
     @staticmethod
     def init_paged_forward_ctx(task_datas: list[TaskData], kvcaches: list[PagedKVCache]) -> "FlashForwardCtx":
-        host = pack_descriptors(task_datas, kvcaches)
         pool = kvcaches[0].pool
-        names = ["indptr", "kv_page_indptr", "kv_last_page_lens", "offsets", "seqlens", "kv_page_indices"]
-        sizes = [len(host[n]) for n in names]
-        starts = np.concatenate([[0], np.cumsum([_ceil4(s) for s in sizes])])
         on_gpu = pool.main_device.type == "cuda"
-        buf = torch.empty(int(starts[-1]), dtype=torch.int32, pin_memory=on_gpu)
-        buf_np = buf.numpy()
-        for n, s, sz in zip(names, starts, sizes):
-            buf_np[s : s + sz] = host[n]
-        dev = buf.to(pool.main_device, non_blocking=True) if on_gpu else buf
-        t = {n: dev[s : s + sz] for n, s, sz in zip(names, starts, sizes)}
-        return FlashForwardCtx(
-            bsz=len(task_datas), seqlens=t["seqlens"], layer_id=0, page_pool=pool, offsets=t["offsets"],
+        bsz = len(task_datas)
+        ps = pool.page_size
+        cap = 5 * (bsz + 4) + sum((t.start_pos + t.seqlen + ps - 1) // ps for t in task_datas) + 4
+        pinned = torch.empty(cap, dtype=torch.int32, pin_memory=on_gpu)
+        _, used, host = build_step(task_datas, kvcaches, pinned.numpy())
+        dev = pinned[:used].to(pool.main_device, non_blocking=True) if on_gpu else pinned
+        starts = {n: host[n].ctypes.data - pinned.data_ptr() for n in _NAMES}
+        t = {n: dev[starts[n] // 4 : starts[n] // 4 + len(host[n])] for n in _NAMES}
+        ctx = FlashForwardCtx(
+            bsz=bsz, seqlens=t["seqlens"], layer_id=0, page_pool=pool, offsets=t["offsets"],
             indptr=t["indptr"], kv_page_indices=t["kv_page_indices"], kv_page_indptr=t["kv_page_indptr"],
             kv_last_page_lens=t["kv_last_page_lens"], host=host)
+        ctx._pinned = pinned  # `host` are views of it
+        return ctx
 
 
 @dataclass

@@ -57,7 +57,6 @@ class PagePool:
     ):
         self.num_layers = num_layers
         self.num_pages = num_pages
-        self.num_avails = num_pages
         self.page_size = page_size
         self.main_device = torch.device(main_device)
         self.main_dtype = main_dtype
@@ -69,7 +68,29 @@ class PagePool:
             (num_layers, num_pages, 2, page_size, n_kv_heads, head_dim), device=self.main_device, dtype=main_dtype
         )
         self._bitmap = np.ones(num_pages, dtype=bool)  # True = free
-        self._buffer = np.zeros(0, dtype=np.int32)  # ids already taken out of the bitmap
+        # ids already taken out of the bitmap: a window (start, length) of a fixed array, so that the
+        # native step builder can work on the same state
+        self._buf_store = np.zeros(max(num_pages, 1), dtype=np.int32)
+        self._buf_win = np.zeros(2, dtype=np.int32)
+        self._avails = np.array([num_pages], dtype=np.int64)
+
+    @property
+    def num_avails(self) -> int:
+        return int(self._avails[0])
+
+    @num_avails.setter
+    def num_avails(self, value: int) -> None:
+        self._avails[0] = value
+
+    @property
+    def _buffer(self) -> np.ndarray:
+        return self._buf_store[self._buf_win[0] : self._buf_win[0] + self._buf_win[1]]
+
+    @_buffer.setter
+    def _buffer(self, ids: np.ndarray) -> None:
+        n = len(ids)
+        self._buf_store[:n] = ids
+        self._buf_win[0], self._buf_win[1] = 0, n
 
     # attributes the reference exposes as tensors
     @property
@@ -78,7 +99,7 @@ class PagePool:
 
     @property
     def page_buffer(self) -> torch.Tensor:
-        return torch.from_numpy(self._buffer)
+        return torch.from_numpy(self._buffer.copy())
 
     @property
     def page_elems(self) -> int:
@@ -106,13 +127,15 @@ class PagePool:
                 got = np.flatnonzero(self._bitmap)[:want].astype(np.int32)
                 self._bitmap[got] = False
                 self._buffer = np.concatenate([self._buffer, got])
-            out, self._buffer = self._buffer[:size], self._buffer[size:]
+            out = self._buffer[:size].copy()
+            self._buf_win[0] += size
+            self._buf_win[1] -= size
             return out
 
     def alloc(self, size: int) -> Optional[torch.Tensor]:
         """`size` page ids as an int32 tensor (host memory). Raises ValueError
         when the pool cannot satisfy the request."""
-        return torch.from_numpy(self._alloc_np(size).copy())
+        return torch.from_numpy(self._alloc_np(size))
 
     def alloc_consecutive(self, size: int) -> Optional[torch.Tensor]:
         """First run of `size` consecutive free pages, or None."""
@@ -197,6 +220,7 @@ class PageTableAllocator:
         self.mutex = threading.Lock()
         self._tables_np = np.zeros((max_requests_num, max_context_len // page_size), dtype=np.int32)
         self.tables = torch.from_numpy(self._tables_np)
+        self._isswap_np = np.zeros(self._tables_np.shape, dtype=bool)  # per entry: page sits in a swap region
         self.slots = list(range(max_requests_num))
 
     def alloc(self) -> PageTableHandle:
@@ -308,7 +332,7 @@ class VirtualPagePool(GpuPagePool):
         incoming region's saved bitmap, save and clear the outgoing one."""
         with self.mutex:
             self._bitmap[self._buffer.astype(np.int64)] = True
-            self._buffer = np.zeros(0, dtype=np.int32)
+            self._buf_win[:] = 0
             on, off = self.on, 1 - self.on
             a, b = self.slices[on]
             c, d = self.slices[off]
@@ -373,11 +397,20 @@ class VirtualPagePool(GpuPagePool):
 class VirtualPagedKVCache(PagedKVCache):
     """PagedKVCache over a VirtualPagePool; remembers which of its pages sit in a
     swap region so they can be shifted when the microbatch changes region
-    (reference: virtual.py:119-161)."""
+    (reference: virtual.py:119-161). The flags live beside the page table row."""
 
     def __init__(self, page_table: PageTableHandle, isswap, pool: VirtualPagePool) -> None:
         super().__init__(page_table, pool)
-        self._isswap = _as_ids(isswap).astype(bool) if not isinstance(isswap, np.ndarray) else isswap
+        row = page_table.allocator._isswap_np[page_table.offset]
+        row[:] = False
+        if isswap is not None:
+            flags = np.asarray(isswap.cpu() if isinstance(isswap, torch.Tensor) else isswap).astype(bool)
+            n = min(len(flags), len(row))
+            row[:n] = flags[:n]
+
+    @property
+    def _isswap(self) -> np.ndarray:
+        return self.page_table.allocator._isswap_np[self.page_table.offset]
 
     @property
     def isswap(self) -> torch.Tensor:
@@ -385,7 +418,7 @@ class VirtualPagedKVCache(PagedKVCache):
 
     @staticmethod
     def empty(allocator: PageTableAllocator, pool: VirtualPagePool) -> "VirtualPagedKVCache":
-        return VirtualPagedKVCache(allocator.alloc(), np.zeros(allocator.max_context_len, dtype=bool), pool)
+        return VirtualPagedKVCache(allocator.alloc(), None, pool)
 
     def extend(self, num_tokens: int) -> bool:
         occ = self.page_table.occupied
@@ -401,8 +434,8 @@ class VirtualPagedKVCache(PagedKVCache):
         row[self._isswap[: self.page_table.occupied]] += offset
 
     def free(self) -> None:
+        self._isswap[:] = False
         super().free()
-        self._isswap = np.zeros(0, dtype=bool)
 
 
 # --------------------------------------------------------------------------
@@ -599,9 +632,7 @@ class KVCacheManager:
             ids = pool._alloc_np(h.initial_size)
             table = self.page_table_allocator.alloc()
             table.extend(ids)
-            isswap = np.zeros(self.page_table_allocator.max_context_len, dtype=bool)
-            isswap[: len(ids)] = ids >= pool.num_pages_main
-            caches.append(VirtualPagedKVCache(table, isswap, pool))
+            caches.append(VirtualPagedKVCache(table, ids >= pool.num_pages_main, pool))
             id_lists.append(ids.copy())
         self._move(False, id_lists, handles)
         return caches

@@ -303,6 +303,33 @@ int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes
                     const void* host_in, void* stream_out, void* stream_in, void* event);
 
 /*
+ * The host half of a step in one native call (no CUDA): for every request of
+ * the batch, grow its page list to max(start_pos + seqlen, initial_seqlen)
+ * tokens — pages come from the prefetch buffer, refilled with the lowest free
+ * indices, at least fetch_size at a time, exactly the reference's order
+ * (deserve_worker/kvcache/paged/page_pool.py:38-55, kvcache.py:21-29,
+ * virtual.py:138-149) — then write the ragged-batch descriptors of
+ * deserve_worker/model/context/flash.py:29-64 into `out` as six 4-int32-aligned
+ * sections: indptr, kv_page_indptr, kv_last_page_lens, offsets, seqlens,
+ * kv_page_indices (section_offsets[0..6], the last entry = int32 used).
+ * All arrays are caller-owned HOST memory: bitmap[num_pages] (1 = free),
+ * buffer[buffer_cap >= num_pages] with the live window (buffer_start,
+ * buffer_len), tables[max_requests, table_cols] and the optional isswap flags
+ * of the same shape (page id >= num_pages_main), slot / occupied per request.
+ * When a request needs more pages than are available the call stops there and
+ * returns DSV_E_WORKSPACE with failed_request / failed_need set (the
+ * reference's ValueError("Not enough pages")); earlier requests stay grown.
+ */
+int dsv_host_build_step(uint8_t* bitmap, int32_t num_pages, int32_t* buffer, int32_t buffer_cap,
+                        int32_t* buffer_start, int32_t* buffer_len, int64_t* num_avails,
+                        int32_t fetch_size, int32_t page_size, int32_t num_pages_main,
+                        int32_t* tables, uint8_t* isswap, int64_t table_cols, int batch,
+                        const int32_t* slot, int32_t* occupied, const int32_t* start_pos,
+                        const int32_t* seqlen, const int32_t* initial_seqlen, int32_t* out,
+                        int64_t out_capacity, int64_t* section_offsets, int32_t* failed_request,
+                        int32_t* failed_need);
+
+/*
  * Self-test of the bounded waits every mbarrier-based kernel here uses: launches
  * one thread that polls (at most `polls` times) a barrier phase nothing will
  * ever complete. The wait gives up, the kernel ends normally and

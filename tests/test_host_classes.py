@@ -11,8 +11,21 @@ from helpers import bits, host_traces
 CPU = torch.device("cpu")
 
 
+def _extend(cache, tokens, native):
+    """Grow a cache through the Python class or through the native step builder."""
+    if not native:
+        return cache.extend(tokens)
+    from deserve_b200.context import build_step
+
+    t = dk.TaskData.empty("x", 0)
+    t.init(tokens)
+    build_step([t], [cache])
+    return True
+
+
+@pytest.mark.parametrize("native", [False, True])
 @pytest.mark.parametrize("idx", [0, 1, 2])
-def test_allocator_trace(idx):
+def test_allocator_trace(idx, native):
     tr = host_traces()["alloc_traces"][idx]
     pool = dk.CpuPagePool(1, tr["num_pages"], tr["page_size"], torch.float16, n_kv_heads=1, head_dim=8)
     pta = dk.PageTableAllocator(tr["max_req"], 4096, tr["page_size"], CPU)
@@ -24,10 +37,10 @@ def test_allocator_trace(idx):
         elif op["op"] == "extend":
             c = live[op["id"]]
             if "error" in op:
-                with pytest.raises(ValueError):
-                    c.extend(op["tokens"])
+                with pytest.raises(ValueError, match="Not enough pages"):
+                    _extend(c, op["tokens"], native)
             else:
-                assert c.extend(op["tokens"]) is True
+                assert _extend(c, op["tokens"], native) is True
                 assert c.page_table.retrieve().tolist() == op["table"]
             assert pool.num_avails == op["num_avails"]
             assert pool.page_buffer.tolist() == op["buffer"]
@@ -69,8 +82,9 @@ def _check_vstate(pool, st):
     assert pool.page_buffer.tolist() == st["buffer"]
 
 
+@pytest.mark.parametrize("native", [False, True])
 @pytest.mark.parametrize("idx", [0, 1, 2])
-def test_virtual_pool_trace(idx):
+def test_virtual_pool_trace(idx, native):
     tr = host_traces()["virtual_traces"][idx]
     pool = dk.VirtualPagePool(1, tr["main"], tr["swap"], tr["page_size"], CPU, torch.float16, n_kv_heads=1, head_dim=8)
     pta = dk.PageTableAllocator(64, 4096, tr["page_size"], CPU)
@@ -98,9 +112,9 @@ def test_virtual_pool_trace(idx):
             c = live[op["id"]]
             if "error" in op:
                 with pytest.raises(ValueError):
-                    c.extend(op["tokens"])
+                    _extend(c, op["tokens"], native)
             else:
-                c.extend(op["tokens"])
+                _extend(c, op["tokens"], native)
                 assert c.page_table.retrieve().tolist() == op["table"]
                 assert c.isswap[: c.page_table.occupied].tolist() == op["isswap"]
             _check_vstate(pool, op["state"])
