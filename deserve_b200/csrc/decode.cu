@@ -315,36 +315,90 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const DecodeParams 
   }
 }
 
-// One warp per (request, q head): fold that request's partial states.
+// One CTA of 128 threads per (request, q head): fold that request's partial states.
+// The weights 2^(m_s - max m) are computed once, cooperatively, into shared memory; then thread d
+// sums its head_dim element over all parts with independent (pipelined) loads. A request cut into
+// hundreds of parts (one long sequence spread over the whole machine) costs a few microseconds.
+constexpr int kMergeThreads = 128;
+constexpr int kMergeChunk = 512;  // parts handled per pass (shared-memory weights)
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kMergeThreads)
 merge_kernel(const int2* __restrict__ merge, const float* __restrict__ part_o,
              const float* __restrict__ part_ml, T* __restrict__ out, float* __restrict__ lse,
              int64_t out_stride, int n_q_heads, int head_dim) {
-  const int req = blockIdx.x;
-  const int qh = blockIdx.y * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (qh >= n_q_heads) return;
+  __shared__ float w[kMergeChunk];
+  __shared__ float red[kMergeThreads / 32];
+  __shared__ float bcast[2];
+  const int req = blockIdx.x, qh = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int2 mi = merge[req];
   if (mi.y <= 1) return;  // written directly by the attention kernel
+  const float* ml = part_ml + ((int64_t)mi.x * n_q_heads + qh) * 2;
+  const int64_t ml_step = (int64_t)n_q_heads * 2;
+  // maximum of the parts' running maxima
   float mx = -INFINITY;
-  for (int s = 0; s < mi.y; ++s) mx = fmaxf(mx, part_ml[((int64_t)(mi.x + s) * n_q_heads + qh) * 2]);
+  for (int s = tid; s < mi.y; s += kMergeThreads) mx = fmaxf(mx, ml[s * ml_step]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float t = red[0];
+    for (int i = 1; i < kMergeThreads / 32; ++i) t = fmaxf(t, red[i]);
+    bcast[0] = t;
+  }
+  __syncthreads();
+  mx = bcast[0];
+  float acc[2] = {0.f, 0.f};  // head_dim <= 256: up to two elements per thread
   float lsum = 0.f;
-  for (int s = 0; s < mi.y; ++s) {
-    const float* ml = part_ml + ((int64_t)(mi.x + s) * n_q_heads + qh) * 2;
-    lsum += (ml[0] == -INFINITY) ? 0.f : ml[1] * exp2f(ml[0] - mx);
-  }
-  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-  for (int d = lane; d < head_dim; d += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < mi.y; ++s) {
-      const float mw = part_ml[((int64_t)(mi.x + s) * n_q_heads + qh) * 2];
-      const float a = (mw == -INFINITY) ? 0.f : exp2f(mw - mx);
-      acc += part_o[((int64_t)(mi.x + s) * n_q_heads + qh) * head_dim + d] * a;
+  for (int s0 = 0; s0 < mi.y; s0 += kMergeChunk) {
+    const int n = min(kMergeChunk, mi.y - s0);
+    __syncthreads();  // w from the previous pass is no longer read
+    for (int s = tid; s < n; s += kMergeThreads) {
+      const float ms = ml[(s0 + s) * ml_step];
+      const float a = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
+      w[s] = a;
+      lsum += ml[(s0 + s) * ml_step + 1] * a;
     }
-    out[(int64_t)req * out_stride + (int64_t)qh * head_dim + d] = from_f32<T>(acc * inv);
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int d = tid + k * kMergeThreads;
+      if (d < head_dim) {
+        const float* po = part_o + ((int64_t)(mi.x + s0) * n_q_heads + qh) * head_dim + d;
+        const int64_t step = (int64_t)n_q_heads * head_dim;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int s = 0;
+        for (; s + 4 <= n; s += 4) {
+          a0 = fmaf(po[(s + 0) * step], w[s + 0], a0);
+          a1 = fmaf(po[(s + 1) * step], w[s + 1], a1);
+          a2 = fmaf(po[(s + 2) * step], w[s + 2], a2);
+          a3 = fmaf(po[(s + 3) * step], w[s + 3], a3);
+        }
+        for (; s < n; ++s) a0 = fmaf(po[s * step], w[s], a0);
+        acc[k] += (a0 + a1) + (a2 + a3);
+      }
+    }
   }
-  if (lse != nullptr && lane == 0)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = lsum;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int i = 0; i < kMergeThreads / 32; ++i) t += red[i];
+    bcast[1] = t;
+  }
+  __syncthreads();
+  lsum = bcast[1];
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int d = tid + k * kMergeThreads;
+    if (d < head_dim) out[(int64_t)req * out_stride + (int64_t)qh * head_dim + d] = from_f32<T>(acc[k] * inv);
+  }
+  if (lse != nullptr && tid == 0)
     lse[(int64_t)req * n_q_heads + qh] = lsum > 0.f ? (mx + log2f(lsum)) * kLn2 : -INFINITY;
 }
 
@@ -601,16 +655,16 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
 
   if (slots > 0) {
     const int2* merge = reinterpret_cast<const int2*>(plan_dev + plan_host[6]);
-    const dim3 mgrid((unsigned)batch, (unsigned)((n_q_heads + 3) / 4));
+    const dim3 mgrid((unsigned)batch, (unsigned)n_q_heads);
     switch (dtype) {
       case DSV_F32:
-        merge_kernel<float><<<mgrid, 128, 0, st>>>(merge, p.part_o, p.part_ml, (float*)out, lse, out_stride_tok, n_q_heads, head_dim);
+        merge_kernel<float><<<mgrid, kMergeThreads, 0, st>>>(merge, p.part_o, p.part_ml, (float*)out, lse, out_stride_tok, n_q_heads, head_dim);
         break;
       case DSV_F16:
-        merge_kernel<__half><<<mgrid, 128, 0, st>>>(merge, p.part_o, p.part_ml, (__half*)out, lse, out_stride_tok, n_q_heads, head_dim);
+        merge_kernel<__half><<<mgrid, kMergeThreads, 0, st>>>(merge, p.part_o, p.part_ml, (__half*)out, lse, out_stride_tok, n_q_heads, head_dim);
         break;
       default:
-        merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, st>>>(merge, p.part_o, p.part_ml, (__nv_bfloat16*)out, lse, out_stride_tok, n_q_heads, head_dim);
+        merge_kernel<__nv_bfloat16><<<mgrid, kMergeThreads, 0, st>>>(merge, p.part_o, p.part_ml, (__nv_bfloat16*)out, lse, out_stride_tok, n_q_heads, head_dim);
     }
     DSV_CUDA(cudaGetLastError());
   }
