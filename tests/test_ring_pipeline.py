@@ -94,3 +94,45 @@ def test_single_rank_ring_is_a_plain_loop():
     pipe = RingPipeline(0, 1, lambda u, m, s, x: x + 1, lambda m: torch.zeros(2), 5)
     pipe.advance(5)
     assert pipe.last_output.tolist() == [5.0, 5.0] and pipe.completed == [(0, s) for s in range(5)]
+
+
+def _dying_worker(rank, world, port, q):
+    """Rank 1 leaves between two slots (host-side failure, nothing in flight); rank 0 must get an
+    error from its next exchange within the process-group timeout instead of waiting forever."""
+    sys.path.insert(0, str(ROOT))
+    import datetime
+    import time
+
+    import torch.distributed as dist
+
+    from deserve_b200.engine import RingPipeline
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    pipe = RingPipeline(rank, world, lambda u, m, s, x: x + 1, lambda m: torch.zeros(3), 50, dist=dist)
+    pipe.advance(4)
+    if rank == 1:
+        dist.destroy_process_group()
+        q.put((rank, "left"))
+        return
+    t0 = time.time()
+    try:
+        pipe.advance(20)
+        q.put((rank, "no error"))
+    except Exception as exc:  # gloo reports the closed / timed-out peer
+        q.put((rank, f"error after {time.time() - t0:.1f}s: {type(exc).__name__}"))
+
+
+def test_a_rank_that_leaves_surfaces_as_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dying_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=90) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert got[1] == "left"
+    assert got[0].startswith("error after"), got[0]
+    assert float(got[0].split()[2][:-2]) < 30.0
