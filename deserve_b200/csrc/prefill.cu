@@ -541,8 +541,8 @@ int ilog2_exact(int x) {
 extern "C" {
 
 int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, int batch, int n_q_heads,
-                     int n_kv_heads, int head_dim, int page_size, int dtype, int causal, int32_t* plan_host,
-                     int64_t plan_capacity_i32, int64_t* plan_used_i32) {
+                     int n_kv_heads, int head_dim, int page_size, int dtype, int causal, int min_new_tokens,
+                     int32_t* plan_host, int64_t plan_capacity_i32, int64_t* plan_used_i32) {
   using namespace dsv;
   DSV_REQUIRE(qo_indptr_host && kv_len_host && plan_host && plan_used_i32, "prefill_plan: null pointer argument");
   DSV_REQUIRE(batch >= 0, "prefill_plan: negative batch");
@@ -556,6 +556,7 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
     const int n = qo_indptr_host[i + 1] - qo_indptr_host[i];
     const int len = kv_len_host[i];
     DSV_REQUIRE(n >= 0 && len >= n, "prefill_plan: request %d has %d new tokens but kv length %d", i, n, len);
+    if (n < min_new_tokens) continue;  // left to another kernel (decode rows of a mixed batch)
     for (int q0 = 0; q0 < n; q0 += 2 * tq) {  // a work item is two q tiles of the same request
       const int nq = std::min(2 * tq, n - q0);
       const int hi = causal ? len - n + q0 + nq : len;  // kv positions the tile's last token sees

@@ -190,7 +190,7 @@ def stage_wrappers(device) -> tuple:
     key = torch.device(device).index or 0
     if key not in _WRAPPERS:
         ws = torch.empty(128 << 20, dtype=torch.uint8, device=device)
-        ws2 = torch.empty(2 << 20, dtype=torch.uint8, device=device)
+        ws2 = torch.empty(64 << 20, dtype=torch.uint8, device=device)
         _WRAPPERS[key] = (ops.BatchDecodeWithPagedKVCacheWrapper(ws), ops.BatchPrefillWithPagedKVCacheWrapper(ws2))
     return _WRAPPERS[key]
 
@@ -260,7 +260,8 @@ class BatchPrefill(BatchExec):
                               paged_kv_last_page_len=c.kv_last_page_lens, num_qo_heads=a.n_heads,
                               num_kv_heads=a.n_kv_heads, head_dim=a.dim // a.n_heads, page_size=c.page_pool.page_size,
                               data_type=c.page_pool.main_dtype, causal=True, qo_indptr_host=c.host["indptr"],
-                              kv_indptr_host=c.host["kv_page_indptr"], last_page_len_host=c.host["kv_last_page_lens"])
+                              kv_indptr_host=c.host["kv_page_indptr"], last_page_len_host=c.host["kv_last_page_lens"],
+                              kv_indices_host=c.host["kv_page_indices"])
 
     def step(self, ignore_eos: bool) -> BatchResult:
         with torch.inference_mode():

@@ -212,14 +212,16 @@ def prefill_plan_capacity(nnz: int, batch: int, group: int) -> int:
 
 
 def make_prefill_plan(qo_indptr_host: np.ndarray, kv_len_host: np.ndarray, n_q_heads: int, n_kv_heads: int,
-                      head_dim: int, page_size: int, dtype: torch.dtype, causal: bool, plan_out: np.ndarray) -> int:
-    """Fill plan_out (int32) with the (request, q tile) work items; returns the int32 entries used."""
+                      head_dim: int, page_size: int, dtype: torch.dtype, causal: bool, plan_out: np.ndarray,
+                      min_new_tokens: int = 0) -> int:
+    """Fill plan_out (int32) with the (request, q tile) work items; returns the int32 entries
+    used. Requests with fewer than min_new_tokens new tokens get no item."""
     qo = np.ascontiguousarray(qo_indptr_host, dtype=np.int32)
     kl = np.ascontiguousarray(kv_len_host, dtype=np.int32)
     used = ctypes.c_int64()
     _lib.check(_lib.lib.dsv_prefill_plan(qo.ctypes.data, kl.ctypes.data, len(kl), n_q_heads, n_kv_heads, head_dim,
-                                         page_size, _lib.dtype_code(dtype), 1 if causal else 0, plan_out.ctypes.data,
-                                         plan_out.size, ctypes.byref(used)))
+                                         page_size, _lib.dtype_code(dtype), 1 if causal else 0, int(min_new_tokens),
+                                         plan_out.ctypes.data, plan_out.size, ctypes.byref(used)))
     return used.value
 
 
@@ -251,9 +253,15 @@ class BatchPrefillWithPagedKVCacheWrapper:
     """begin_forward / forward / end_forward object of the reference's prefill path
     (exec.py:22, 227-242; attention.py:188-192): ragged causal attention of the
     step's new q rows against the paged K/V, also used for mixed prefill+decode
-    batches. The head of `workspace_buffer` holds the device copy of the plan."""
+    batches. In a mixed batch the rows of requests with ONE new token (plain decode
+    rows; causal attention of a single last row is unmasked attention) are sent to
+    the decode kernel, which streams their K/V at HBM speed, and only the prompt
+    chunks go to the tensor-core prefill kernel; both write into the same output.
+    The head of `workspace_buffer` holds the device copies of the plans and of the
+    decode rows' sub-descriptors, the rest the split-KV partial states."""
 
     _PLAN_BYTES = 1 << 20
+    SPLIT_MIN_KV = 64  # a decode row with at least this many kv tokens makes the second launch worth it
 
     def __init__(self, workspace_buffer: torch.Tensor, kv_layout: str = "NHD"):
         _lib.require_cuda(workspace_buffer)
@@ -262,17 +270,19 @@ class BatchPrefillWithPagedKVCacheWrapper:
         if workspace_buffer.dtype != torch.uint8 or workspace_buffer.numel() < self._PLAN_BYTES:
             raise ValueError("workspace_buffer must be a uint8 tensor of at least 1 MiB")
         self._ws = workspace_buffer
+        self._sm_count = _lib.device_info()[0]
         self._plan_host: np.ndarray | None = None
         self._pinned = None
         self._desc = None
+        self._dec = None
 
     def begin_forward(self, qo_indptr: torch.Tensor, paged_kv_indptr: torch.Tensor, paged_kv_indices: torch.Tensor,
                       paged_kv_last_page_len: torch.Tensor, num_qo_heads: int, num_kv_heads: int, head_dim: int,
                       page_size: int, data_type=torch.float16, causal: bool = True, *,
                       qo_indptr_host: np.ndarray | None = None, kv_indptr_host: np.ndarray | None = None,
-                      last_page_len_host: np.ndarray | None = None) -> None:
+                      last_page_len_host: np.ndarray | None = None, kv_indices_host: np.ndarray | None = None) -> None:
         """Plan the q tiles of this batch. The *_host arrays (same values as the
-        device tensors) avoid three device->host copies."""
+        device tensors) avoid device->host copies."""
         if qo_indptr_host is None:
             qo_indptr_host = qo_indptr.cpu().numpy()
         if kv_indptr_host is None:
@@ -281,16 +291,61 @@ class BatchPrefillWithPagedKVCacheWrapper:
             last_page_len_host = paged_kv_last_page_len.cpu().numpy()
         n_pages = np.diff(kv_indptr_host)
         kv_len = np.where(n_pages > 0, (n_pages - 1) * page_size + last_page_len_host, 0).astype(np.int32)
+        n_new = np.diff(qo_indptr_host)
         batch, nnz = len(kv_len), int(qo_indptr_host[-1])
-        cap = prefill_plan_capacity(nnz, batch, num_qo_heads // num_kv_heads)
-        if cap * 4 > self._PLAN_BYTES:
-            raise _lib.DeserveKVError(f"prefill plan for {nnz} tokens does not fit the workspace head")
-        pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
         dtype = data_type if isinstance(data_type, torch.dtype) else torch.float16
+        # decode rows of a mixed batch go to the decode kernel
+        # (all of them or none: the prefill plan then skips every request with a single new token)
+        dec = np.flatnonzero(n_new == 1) if causal else np.zeros(0, dtype=np.int64)
+        split = (len(dec) > 0 and int(kv_len[dec].max()) >= self.SPLIT_MIN_KV
+                 and self._ws.numel() >= 4 * self._PLAN_BYTES)
+        cap = prefill_plan_capacity(nnz, batch, num_qo_heads // num_kv_heads)
+        dec_cap = 0
+        if split:
+            if kv_indices_host is None:
+                kv_indices_host = paged_kv_indices.cpu().numpy()
+            sub_pages = n_pages[dec]
+            sub_indptr = np.zeros(len(dec) + 1, dtype=np.int32)
+            np.cumsum(sub_pages, out=sub_indptr[1:])
+            # sections: prefill plan | decode plan | sub indptr | sub last | q rows | sub indices
+            dec_cap = plan_capacity(len(dec), self._sm_count)
+            total = cap + dec_cap + 3 * (len(dec) + 4) + int(sub_indptr[-1]) + 16
+        else:
+            total = cap
+        if total * 4 > self._PLAN_BYTES:
+            if split:  # too many decode rows for the workspace head: keep them in the prefill kernel
+                split, total = False, cap
+            if cap * 4 > self._PLAN_BYTES:
+                raise _lib.DeserveKVError(f"prefill plan for {nnz} tokens does not fit the workspace head")
+        pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        buf = pinned.numpy()
         used = make_prefill_plan(qo_indptr_host, kv_len, num_qo_heads, num_kv_heads, head_dim, page_size, dtype, causal,
-                                 pinned.numpy())
-        self._ws[: used * 4].view(torch.int32).copy_(pinned[:used], non_blocking=True)
-        self._pinned, self._plan_host = pinned, pinned.numpy()
+                                 buf[:cap], min_new_tokens=2 if split else 0)
+        self._dec = None
+        end = used
+        if split:
+            a4 = lambda n: (n + 3) & ~3
+            o_plan = a4(used)
+            d_used, ws_bytes = make_decode_plan(sub_indptr, num_qo_heads, num_kv_heads, head_dim, page_size, dtype,
+                                                self._sm_count, buf[o_plan : o_plan + dec_cap])
+            if ws_bytes > self._ws.numel() - self._PLAN_BYTES:
+                raise _lib.DeserveKVError(f"workspace_buffer too small: split-KV partials need {ws_bytes} bytes")
+            o_ip = a4(o_plan + d_used)
+            o_last = a4(o_ip + len(dec) + 1)
+            o_rows = a4(o_last + len(dec))
+            o_idx = a4(o_rows + len(dec))
+            end = o_idx + int(sub_indptr[-1])
+            buf[o_ip : o_ip + len(dec) + 1] = sub_indptr
+            buf[o_last : o_last + len(dec)] = last_page_len_host[dec]
+            buf[o_rows : o_rows + len(dec)] = qo_indptr_host[dec]        # the single new row of each decode request
+            starts = kv_indptr_host[dec]
+            pos = 0
+            for s0, n in zip(starts.tolist(), sub_pages.tolist()):
+                buf[o_idx + pos : o_idx + pos + n] = kv_indices_host[s0 : s0 + n]
+                pos += n
+            self._dec = (o_plan, d_used, o_ip, o_last, o_rows, o_idx, len(dec), int(sub_indptr[-1]), buf[o_plan : o_plan + d_used])
+        self._ws[: end * 4].view(torch.int32).copy_(pinned[:end], non_blocking=True)
+        self._pinned, self._plan_host = pinned, buf
         self._desc = (qo_indptr, paged_kv_indptr, paged_kv_indices, paged_kv_last_page_len, num_qo_heads, head_dim, causal)
 
     def forward(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, causal: bool = True, sm_scale: float | None = None,
@@ -302,11 +357,23 @@ class BatchPrefillWithPagedKVCacheWrapper:
             raise ValueError("forward(causal=...) differs from the value given to begin_forward")
         if q.dim() == 2:
             q = q.view(-1, hq, d)
-        return paged_prefill(q, qo, paged_kv_cache, kv_indices, kv_indptr, last, self._plan_host,
-                             self._ws[: self._PLAN_BYTES].view(torch.int32), out, sm_scale, causal)
+        head = self._ws[: self._PLAN_BYTES].view(torch.int32)
+        if out is None:
+            out = torch.empty((q.shape[0], hq, d), dtype=q.dtype, device=q.device)
+        if self._plan_host[1] > 0:
+            paged_prefill(q, qo, paged_kv_cache, kv_indices, kv_indptr, last, self._plan_host, head, out, sm_scale, causal)
+        if self._dec is not None:
+            o_plan, d_used, o_ip, o_last, o_rows, o_idx, n_dec, n_idx, plan_host = self._dec
+            rows = head[o_rows : o_rows + n_dec].long()
+            out_dec = paged_decode(q.index_select(0, rows), paged_kv_cache, head[o_idx : o_idx + n_idx],
+                                   head[o_ip : o_ip + n_dec + 1], head[o_last : o_last + n_dec], plan_host,
+                                   head[o_plan : o_plan + d_used], self._ws[self._PLAN_BYTES :], sm_scale=sm_scale)
+            out.index_copy_(0, rows, out_dec)
+        return out
 
     def end_forward(self) -> None:
         self._desc = None
+        self._dec = None
 
 
 def rope_append_paged_kv_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, indptr: torch.Tensor,

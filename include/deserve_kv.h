@@ -179,12 +179,14 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
  * kv_len_host[batch] (HOST memory; kv_len = post-append length of each
  * request) and writes the list of (request, q-tile) work items: a tile holds
  * 128 / (n_q_heads / n_kv_heads) q tokens and knows how many kv positions its
- * last token sees (all of them when causal = 0). Pure host arithmetic.
+ * last token sees (all of them when causal = 0). Requests with fewer than
+ * min_new_tokens new tokens get no work item (a caller that sends the decode
+ * rows of a mixed batch to dsv_paged_decode passes 2). Pure host arithmetic.
  */
 int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, int batch,
                      int n_q_heads, int n_kv_heads, int head_dim, int page_size, int dtype,
-                     int causal, int32_t* plan_host, int64_t plan_capacity_i32,
-                     int64_t* plan_used_i32);
+                     int causal, int min_new_tokens, int32_t* plan_host,
+                     int64_t plan_capacity_i32, int64_t* plan_used_i32);
 
 /*
  * Ragged causal attention of nnz new q rows against paged K/V (chunked

@@ -42,7 +42,7 @@ def _run(seed, kv_lens, new_tokens, hq, hkv, d, ps, dtype, causal=True, poison=F
     nnz = int(desc["indptr"][-1])
     q = torch.randn(nnz, hq, d, generator=g).to(dtype)
     want = kv_math.paged_attention(q, pages, desc, ps, causal=causal)
-    ws = torch.empty(4 << 20, dtype=torch.uint8, device=DEV)
+    ws = torch.empty(32 << 20, dtype=torch.uint8, device=DEV)
     wrapper = dk.BatchPrefillWithPagedKVCacheWrapper(ws)
     dd = to_device(desc, DEV)
     wrapper.begin_forward(dd["indptr"], dd["kv_page_indptr"], dd["kv_page_indices"], dd["kv_last_page_lens"], hq, hkv, d,
@@ -71,7 +71,24 @@ def test_chunked_prefill_on_existing_context(hq, hkv, d, ps):
 
 
 def test_mixed_prefill_and_decode_rows():
-    err, _ = _run(3, [2000, 17, 900, 1, 333], [1, 17, 1, 1, 200], 32, 8, 128, 16, torch.bfloat16, poison=True)
+    # rows with one new token and a long context go to the decode kernel, the chunks to the prefill kernel
+    err, _ = _run(3, [2000, 17, 900, 1, 333, 4000], [1, 17, 1, 1, 200, 1], 32, 8, 128, 16, torch.bfloat16, poison=True)
+    assert err <= 2e-2, f"max-abs error {err}"
+
+
+def test_all_rows_are_decode_rows_through_the_prefill_wrapper():
+    err, _ = _run(8, [300, 64, 1500], [1, 1, 1], 32, 8, 128, 16, torch.bfloat16, poison=True)
+    assert err <= 2e-2, f"max-abs error {err}"
+
+
+def test_small_workspace_keeps_decode_rows_in_the_prefill_kernel():
+    import deserve_b200.ops as o
+    saved = o.BatchPrefillWithPagedKVCacheWrapper.SPLIT_MIN_KV
+    o.BatchPrefillWithPagedKVCacheWrapper.SPLIT_MIN_KV = 1 << 30  # never split: the tensor-core kernel handles n = 1 rows too
+    try:
+        err, _ = _run(3, [2000, 17, 900, 1, 333], [1, 17, 1, 1, 200], 32, 8, 128, 16, torch.bfloat16, poison=True)
+    finally:
+        o.BatchPrefillWithPagedKVCacheWrapper.SPLIT_MIN_KV = saved
     assert err <= 2e-2, f"max-abs error {err}"
 
 
