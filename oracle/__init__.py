@@ -17,10 +17,12 @@ Parity pin: the integer paths (allocator order, page tables, descriptors,
 region state machine, buddy pool, offload chunk layout) and the dense fp32
 attention + rotary math are pinned against outputs of the reference's own
 classes run on CPU (tests/golden/make_golden.py imports them from the
-reference tree and writes tests/golden/*.json|npz). The paged append and the
-paged attention kernels exist in the reference only as calls into the
-third-party flashinfer package (unpinned version, no tests in the reference):
-for those two the oracle states the call semantics (index rule + the dense
-attention math applied to K/V gathered through the page table) and parity at
-that boundary is "unpinned".
+reference tree and writes tests/golden/*.json|npz). The paged append, the
+paged attention kernels, the in-place rotary embedding and RMSNorm exist in
+the reference only as calls into the third-party flashinfer package (version
+not pinned, no tests in the reference): the oracle states their call
+semantics (index rule + the dense attention math applied to K/V gathered
+through the page table) and is pinned at that boundary against results
+recorded from flashinfer 0.6.11 itself on a B200
+(tests/golden/make_flashinfer_golden.py -> tests/golden/flashinfer_golden.*).
 """
