@@ -16,8 +16,9 @@
 //                    (tokens are the K dimension), accumulator O in TMEM
 // The two q tiles ping-pong: while one tile's warp group does its softmax, the tensor
 // core runs the other tile's P V and next Q K^T. Warp 8 is the TMA producer of q and
-// the K ring, warp 10 of the V ring (2 stages each, one cp.async.bulk.tensor per
-// 16-token box and 64-element half of head_dim), warp 9 issues the MMAs from one
+// the K ring (2 stages), warp 10 of the V ring (3 stages: a V slot is released later in
+// a tile's life than a K slot and is wanted first in the next one; one
+// cp.async.bulk.tensor per 16-token box and 64-element half of head_dim), warp 9 issues the MMAs from one
 // thread and signals completion with tcgen05.commit on mbarriers. Every wait is
 // bounded; on expiry the kernel records ST_WAIT_TIMEOUT, leaves the loops, frees its
 // TMEM and returns.
@@ -33,6 +34,7 @@ namespace dsv {
 namespace {
 
 constexpr int kBN = 128;                 // kv tokens per tile
+constexpr int kVStages = 3;                // V tiles in flight (K: 2)
 constexpr int kThreads = 352;            // 2 x 4 softmax warps, K producer, MMA warp, V producer
 constexpr int kSpinLimit = 1 << 21;
 constexpr int32_t kPrefillMagic = 0x44535032;  // "DSP2"
@@ -180,6 +182,11 @@ __host__ __device__ constexpr uint32_t instr_desc(int ab_format, int b_mn_major,
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ float ex2(float x) {  // 2^x on the special-function unit; ex2(-inf) = 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -222,12 +229,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base;                       // 2 q tiles
   const uint32_t k_smem = q_smem + 2 * QTILE;         // 2 stages
-  const uint32_t v_smem = k_smem + 2 * KVTILE;        // 2 stages
-  const uint32_t bars = v_smem + 2 * KVTILE;
-  // barrier slots (8 bytes each): q, kfull[2], vfull[2], kempty[2], vempty[2], sfull[2 tiles], pfull[2], odone[2]
-  const uint32_t bar_q = bars, bar_kfull = bars + 8, bar_vfull = bars + 24, bar_kempty = bars + 40,
-                 bar_vempty = bars + 56, bar_sfull = bars + 72, bar_pfull = bars + 88, bar_odone = bars + 104;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 120);
+  const uint32_t v_smem = k_smem + 2 * KVTILE;        // kVStages stages
+  const uint32_t bars = v_smem + kVStages * KVTILE;
+  // barrier slots (8 bytes each): q, kfull[2], vfull[3], kempty[2], vempty[3], sfull[2 tiles], pfull[2], odone[2]
+  const uint32_t bar_q = bars, bar_kfull = bars + 8, bar_vfull = bars + 24, bar_kempty = bars + 48,
+                 bar_vempty = bars + 64, bar_sfull = bars + 88, bar_pfull = bars + 104, bar_odone = bars + 120;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 136);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.n_q_heads / p.n_kv_heads;
@@ -252,13 +259,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(bar_vfull + 8 * s, 1);
+      mbar_init(bar_vempty + 8 * s, 1);
+    }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_kfull + 8 * s, 1);
-      mbar_init(bar_vfull + 8 * s, 1);
       mbar_init(bar_kempty + 8 * s, 1);
-      mbar_init(bar_vempty + 8 * s, 1);
       mbar_init(bar_sfull + 8 * s, 1);
-      mbar_init(bar_pfull + 8 * s, 128);
+      mbar_init(bar_pfull + 8 * s, 4);  // one arrival per softmax warp
       mbar_init(bar_odone + 8 * s, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -285,8 +294,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
     const int32_t* idx = p.kv_indices + ip0;
     const int kv = warp == 10 ? 1 : 0;
+    const int n_stages = kv ? kVStages : 2;
     for (int tile = 0; tile < n_tiles; ++tile) {
-      const int s = tile & 1;
+      const int s = tile % n_stages, round = tile / n_stages;
       const int t0 = tile * kBN;
       int live = 0;  // boxes that hold at least one visible token
       for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
@@ -294,7 +304,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       // as soon as Q K^T of two tiles ago has run, so the next K tile is in flight long before the
       // MMA warp asks for it, whatever the V ring is waiting for.
       const uint32_t full = (kv ? bar_vfull : bar_kfull) + 8 * s, empty = (kv ? bar_vempty : bar_kempty) + 8 * s;
-      if (tile >= 2 && !warp_wait(empty, ((tile >> 1) - 1) & 1, p.status)) break;
+      if (round > 0 && !warp_wait(empty, (round - 1) & 1, p.status)) break;
       if (lane == 0) mbar_expect_tx(full, (uint32_t)(live * DH * bt * 128));
       __syncwarp();
       for (int b = lane; b < n_boxes; b += 32) {
@@ -323,7 +333,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       // single lane: every instruction it spends per MMA is on the critical path of the tensor core.
       const uint64_t qd[2] = {smem_desc(q_smem, 16, 1024), smem_desc(q_smem + QTILE, 16, 1024)};
       const uint64_t kd[2] = {smem_desc(k_smem, 16, 1024), smem_desc(k_smem + KVTILE, 16, 1024)};
-      const uint64_t vd[2] = {smem_desc(v_smem, HALF_ROWS, 1024), smem_desc(v_smem + KVTILE, HALF_ROWS, 1024)};
+      const uint64_t vd0 = smem_desc(v_smem, HALF_ROWS, 1024);
       auto issue_qk = [&](int tile, int x) {  // S_x = Q_x K_tile^T
         const int s = tile & 1;
         const uint32_t d = tmem + x * COL_TILE + COL_S;
@@ -339,11 +349,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         if (x == (has_b ? 1 : 0)) tc_commit(bar_kempty + 8 * s);  // last reader of this K stage
       };
       auto issue_pv = [&](int tile, int x) {  // O_x += P_x V_tile
-        const int s = tile & 1;
+        const int s = tile % kVStages;
         const int cols = min(kBN, kv_hi - tile * kBN);
         const int ksteps = (cols + 15) >> 4;  // 16-token steps that hold a visible token
         const uint32_t d = tmem + x * COL_TILE + COL_O, a = tmem + x * COL_TILE + COL_S;
-        const uint64_t vb = vd[s];
+        const uint64_t vb = vd0 + (uint64_t)(s * (KVTILE / 16));
         if (ksteps == kBN / 16 && tile > 0) {  // the common case, fully unrolled
 #pragma unroll
           for (int kt = 0; kt < kBN / 16; ++kt) umma_ts_acc(d, a + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV);
@@ -365,7 +375,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         const bool more = tile + 1 < n_tiles;
         for (int x = 0; ok && x < (has_b ? 2 : 1); ++x) {
           ok = mbar_wait(bar_pfull + 8 * x, tile & 1, p.status);
-          if (ok && x == 0) ok = mbar_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status);
+          if (ok && x == 0) ok = mbar_wait(bar_vfull + 8 * (tile % kVStages), (tile / kVStages) & 1, p.status);
           if (!ok) break;
           tc_fence_after();
           issue_pv(tile, x);
@@ -410,13 +420,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           for (int i = 0; i < kBN; ++i)
             if (t0 + i > limit) r[i] = 0xff800000u;  // -inf
         }
-        {  // eight independent chains instead of one 128-long dependent one
+        {  // eight independent chains of three-input maxima instead of one 128-long dependent chain
           float m8[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(r[i]);
 #pragma unroll
-          for (int i = 8; i < kBN; ++i) m8[i & 7] = fmaxf(m8[i & 7], __uint_as_float(r[i]));
-          mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+          for (int i = 8; i + 15 < kBN; i += 16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              m8[j] = fmax3(m8[j], __uint_as_float(r[i + 2 * j]), __uint_as_float(r[i + 2 * j + 1]));
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) m8[j] = fmaxf(m8[j], __uint_as_float(r[kBN - 8 + j]));  // 8 + 7 * 16 = 120 done
+          mx = fmaxf(fmax3(m8[0], m8[1], m8[2]), fmaxf(fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
         }
         const float m_tile = mx * sc;
         // lazy rescale: keep the old reference maximum unless the row maximum grew by more than 2^8
@@ -425,9 +441,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_tile);
           m_used = m_tile;
         }
-        if (tile > 0) {  // O is free once the previous P.V has completed
-          if (!warp_wait(bar_odone + 8 * x, (tile - 1) & 1, p.status)) { ok = false; break; }
-          tc_fence_after();
+        if (tile > 0) {
+          // O is free: S of this tile was issued behind the previous P V and completions are in
+          // issue order, so seeing this S means that P V has finished. No wait needed.
           if (__any_sync(0xffffffffu, factor != 1.f)) {
             l *= factor;
 #pragma unroll 1
@@ -464,17 +480,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         // warp groups write the same zeros; each does it before releasing its own P.
         const int cols = min(kBN, kv_hi - t0);
         if (cols < kBN && (cols & 15) != 0) {
-          if (!warp_wait(bar_vfull + 8 * s, (tile >> 1) & 1, p.status)) { ok = false; break; }
+          const int vs = tile % kVStages;
+          if (!warp_wait(bar_vfull + 8 * vs, (tile / kVStages) & 1, p.status)) { ok = false; break; }
           const int r0 = cols, r1 = (cols + 15) & ~15;
           for (int z = row; z < (r1 - r0) * DH * 8; z += 128) {
             const int ch = z & 7, dh = (z >> 3) % DH, rr = r0 + (z >> 3) / DH;
-            *reinterpret_cast<uint4*>(smem + (v_smem - base) + s * KVTILE + dh * HALF_ROWS + rr * 128 + ch * 16) =
+            *reinterpret_cast<uint4*>(smem + (v_smem - base) + vs * KVTILE + dh * HALF_ROWS + rr * 128 + ch * 16) =
                 make_uint4(0, 0, 0, 0);
           }
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         }
         tc_fence_before();
-        mbar_arrive(bar_pfull + 8 * x);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pfull + 8 * x);
       }
       if (ok) ok = warp_wait(bar_odone + 8 * x, (n_tiles - 1) & 1, p.status);
       if (ok) {
@@ -647,7 +665,7 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
   p.out_stride = out_stride_tok; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.ps_log2 = ps_log2;
   p.num_pages = (int)num_pages; p.causal = causal ? 1 : 0; p.scale_log2 = sm_scale * kLog2e;
   p.status = device_status_ptr();
-  const size_t smem = (size_t)2 * 128 * head_dim * 2 + 4 * (size_t)kBN * head_dim * 2 + 128 + 1024;
+  const size_t smem = (size_t)2 * 128 * head_dim * 2 + (size_t)(2 + kVStages) * kBN * head_dim * 2 + 256 + 1024;
   const dim3 grid((unsigned)n_items, (unsigned)n_kv_heads);
   auto go = [&](auto kernel) -> cudaError_t {
     cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
