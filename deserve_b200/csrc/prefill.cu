@@ -404,7 +404,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       float m_used = -INFINITY, l = 0.f;
       bool ok = true;
       for (int tile = 0; tile < n_tiles; ++tile) {
-        const int s = tile & 1;
         if (!warp_wait(bar_sfull + 8 * x, tile & 1, p.status)) { ok = false; break; }
         tc_fence_after();
         const int t0 = tile * kBN;
