@@ -193,6 +193,19 @@ __device__ __forceinline__ float ex2(float x) {  // 2^x on the special-function 
   return y;
 }
 
+// Packed fp32 pairs: one instruction for two columns of a row. The softmax warps are bound by how
+// many instructions they issue per score, not by the special-function unit alone.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n .reg .b64 a, b, c, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n mov.b64 c, {%6, %7};\n"
+      " fma.rn.f32x2 d, a, b, c;\n mov.b64 {%0, %1}, d;\n}\n"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n .reg .b64 a, b, d;\n mov.b64 a, {%2, %3};\n mov.b64 b, {%4, %5};\n add.rn.f32x2 d, a, b;\n mov.b64 {%0, %1}, d;\n}\n"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <>
@@ -373,16 +386,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       for (int tile = 0; ok && tile < n_tiles; ++tile) {
         const int s = tile & 1;
         const bool more = tile + 1 < n_tiles;
+        // This tile's V and the next tile's K landed long ago (the rings run ahead): look at their
+        // barriers now, while the softmax warps are still busy, not between two products.
+        ok = mbar_wait(bar_vfull + 8 * (tile % kVStages), (tile / kVStages) & 1, p.status);
+        if (ok && more) ok = mbar_wait(bar_kfull + 8 * (s ^ 1), ((tile + 1) >> 1) & 1, p.status);
         for (int x = 0; ok && x < (has_b ? 2 : 1); ++x) {
           ok = mbar_wait(bar_pfull + 8 * x, tile & 1, p.status);
-          if (ok && x == 0) ok = mbar_wait(bar_vfull + 8 * (tile % kVStages), (tile / kVStages) & 1, p.status);
           if (!ok) break;
           tc_fence_after();
           issue_pv(tile, x);
           if (more) {
-            if (x == 0) ok = mbar_wait(bar_kfull + 8 * (s ^ 1), ((tile + 1) >> 1) & 1, p.status);
-            if (!ok) break;
-            tc_fence_after();
             issue_qk(tile + 1, x);  // runs after P_x V (in issue order), so S_x / P_x may be overwritten
           }
         }
@@ -464,10 +477,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float a = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i]), sc, -off));
-            const float b = ex2(fmaf(__uint_as_float(r[c * 32 + 2 * i + 1]), sc, -off));
-            ls[(2 * i) & 3] += a;
-            ls[(2 * i + 1) & 3] += b;
+            float x0, x1, a, b;
+            ffma2(x0, x1, __uint_as_float(r[c * 32 + 2 * i]), __uint_as_float(r[c * 32 + 2 * i + 1]), sc, sc, -off, -off);
+            a = ex2(x0);
+            b = ex2(x1);
+            fadd2(ls[2 * (i & 1)], ls[2 * (i & 1) + 1], ls[2 * (i & 1)], ls[2 * (i & 1) + 1], a, b);
             pk[i] = pack2<T>(a, b);
           }
           tmem_st16(s_addr + c * 16, pk);
