@@ -61,6 +61,9 @@ def parse_args():
     ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (16 GiB of scattered pages out and back)")
     ap.add_argument("--swap-seqs", type=int, default=64)
     ap.add_argument("--swap-tokens", type=int, default=2048)
+    ap.add_argument("--compare-library", action="store_true",
+                    help="only time flashinfer (the library the reference calls) and this package on the same "
+                         "one-layer decode and chunked-prefill inputs; prints its own JSON line")
     return ap.parse_args()
 
 
@@ -287,6 +290,81 @@ def prefill_measure(dk, args, dev, iters=5):
             "bound": "tensor"}
 
 
+def library_compare(dk, args, dev, iters=20):
+    """flashinfer's paged decode / prefill wrappers (what the reference calls) and this package's on the
+    same tensors: one layer of the benchmark's decode shape and the chunked-prefill case. Plans are made
+    outside the timed loops on both sides; K/V read per decode launch is far larger than L2."""
+    import flashinfer as fi
+    from deserve_b200 import ops
+
+    ps, hq, hkv, d = args.page_size, args.q_heads, args.kv_heads, args.head_dim
+    out = {"flashinfer": fi.__version__}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def case(lens, new):
+        n_pages = (lens + ps - 1) // ps
+        total = int(n_pages.sum())
+        pool_pages = int(total * 1.25) + 1
+        g = torch.Generator(device=dev).manual_seed(7)
+        pages = torch.empty(pool_pages, 2, ps, hkv, d, dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+        q = torch.randn(int(new.sum()), hq, d, device=dev, generator=g).to(torch.bfloat16)
+        host = {"qo": np.concatenate([[0], np.cumsum(new)]).astype(np.int32),
+                "kvp": np.concatenate([[0], np.cumsum(n_pages)]).astype(np.int32),
+                "idx": np.random.default_rng(3).permutation(pool_pages)[:total].astype(np.int32),
+                "last": ((lens - 1) % ps + 1).astype(np.int32)}
+        return pages, q, host, {k: torch.from_numpy(v).to(dev) for k, v in host.items()}
+
+    ws_fi = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ws = torch.empty(128 << 20, dtype=torch.uint8, device=dev)
+    # decode: one layer of the benchmark batch
+    lens = make_lengths(args).astype(np.int64)
+    pages, q, host, t = case(lens, np.ones(len(lens), dtype=np.int64))
+    alg = algorithmic_bytes_per_layer(int(lens.sum()), int(((lens + ps - 1) // ps).sum()), args)
+    w = fi.BatchDecodeWithPagedKVCacheWrapper(ws_fi, "NHD")
+    w.plan(t["kvp"], t["idx"], t["last"], hq, hkv, d, ps, pos_encoding_mode="NONE", q_data_type=torch.bfloat16,
+           kv_data_type=torch.bfloat16)
+    ref = w.run(q, pages)
+    ms_fi = timed(lambda: w.run(q, pages))
+    mine = dk.BatchDecodeWithPagedKVCacheWrapper(ws)
+    mine.begin_forward(t["kvp"], t["idx"], t["last"], hq, hkv, d, ps, data_type=torch.bfloat16, indptr_host=host["kvp"])
+    got = mine.forward(q, pages)
+    ms_us = timed(lambda: mine.forward(q, pages))
+    out["decode"] = {"workload": f"{len(lens)} sequences U[{args.ctx_lo},{args.ctx_hi}], one layer",
+                     "flashinfer_ms": ms_fi, "ours_ms": ms_us, "flashinfer_GBps": alg / ms_fi / 1e6,
+                     "ours_GBps": alg / ms_us / 1e6, "max_abs_diff": (got.float() - ref.float()).abs().max().item()}
+    del pages, q
+    # chunked prefill
+    B, ctx, n = args.prefill_reqs, args.prefill_ctx, args.prefill_chunk
+    lens = np.full(B, ctx + n, dtype=np.int64)
+    pages, q, host, t = case(lens, np.full(B, n, dtype=np.int64))
+    flops = 4.0 * hq * d * B * sum(ctx + j + 1 for j in range(n))
+    wp = fi.BatchPrefillWithPagedKVCacheWrapper(ws_fi, "NHD")
+    wp.plan(t["qo"], t["kvp"], t["idx"], t["last"], hq, hkv, d, ps, causal=True, pos_encoding_mode="NONE",
+            q_data_type=torch.bfloat16, kv_data_type=torch.bfloat16)
+    ref = wp.run(q, pages)
+    ms_fi = timed(lambda: wp.run(q, pages))
+    minep = dk.BatchPrefillWithPagedKVCacheWrapper(ws)
+    minep.begin_forward(t["qo"], t["kvp"], t["idx"], t["last"], hq, hkv, d, ps, data_type=torch.bfloat16,
+                        qo_indptr_host=host["qo"], kv_indptr_host=host["kvp"], last_page_len_host=host["last"])
+    got = minep.forward(q, pages, causal=True)
+    ms_us = timed(lambda: minep.forward(q, pages, causal=True))
+    out["prefill"] = {"workload": f"{B} requests x ({ctx} context + {n}-token chunk), causal, one layer",
+                      "flashinfer_ms": ms_fi, "ours_ms": ms_us, "flashinfer_TFLOPs": flops / ms_fi / 1e9,
+                      "ours_TFLOPs": flops / ms_us / 1e9, "max_abs_diff": (got.float() - ref.float()).abs().max().item()}
+    return out
+
+
 def swap_stress(dk, pool, free_ids, args, dev, decode_step):
     """KV swap stress: the KV of swap_seqs x swap_tokens tokens, all layers, scattered over the
     permuted pool, is swapped out to pinned host chunks and back into DIFFERENT pages while decode
@@ -362,6 +440,10 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.compare_library:
+        torch.cuda.set_device(local)
+        print(json.dumps({"library_comparator": library_compare(dk, args, torch.device("cuda", local))}), flush=True)
+        return
     if args.prefill_only:
         torch.cuda.set_device(local)
         print(json.dumps({"prefill": prefill_measure(dk, args, torch.device("cuda", local))}), flush=True)
@@ -502,8 +584,12 @@ def run_ours(args):
     if world == 1 and not args.no_e2e:
         tasks, caches = mbs[0]
         e2e_steps = K
-        hk = torch.randn(L, B, hkv, d).mul_(0.5).to(torch.bfloat16).pin_memory()
-        hv = torch.randn(L, B, hkv, d).mul_(0.5).to(torch.bfloat16).pin_memory()
+        # new K/V rows of every layer in pinned host memory: [layer, K|V, sequence, kv head, head_dim]
+        hkv_host = torch.randn(L, 2, B, hkv, d).mul_(0.5).to(torch.bfloat16).pin_memory()
+        dkv = torch.empty(L, 2, B, hkv, d, dtype=torch.bfloat16, device=dev)
+        copy_stream = torch.cuda.Stream(device=dev)
+        layer_ready = [torch.cuda.Event() for _ in range(L)]
+        step_done = torch.cuda.Event()
         hq_host = torch.randn(B, hq, d).to(torch.bfloat16).pin_memory()
         hout = torch.empty(B, hq, d, dtype=torch.bfloat16).pin_memory()
         ws = torch.empty(128 << 20, dtype=torch.uint8, device=dev)
@@ -512,18 +598,26 @@ def run_ours(args):
         desc_bytes = [0]
 
         def e2e_step():
-            dk_k = hk.to(dev, non_blocking=True)
-            dk_v = hv.to(dev, non_blocking=True)
+            # Layer l's rows are uploaded on a copy stream while earlier layers compute; the compute
+            # stream waits for each layer's event, the copy stream for the previous step's last read.
+            main = torch.cuda.current_stream()
+            copy_stream.wait_event(step_done)
+            with torch.cuda.stream(copy_stream):
+                for layer in range(L):
+                    dkv[layer].copy_(hkv_host[layer], non_blocking=True)
+                    layer_ready[layer].record(copy_stream)
             x = hq_host.to(dev, non_blocking=True)
             ctx = dk.FlashDecodeCtx.init_paged_decode_ctx(tasks, caches, wrapper)
             wrapper.begin_forward(ctx.kv_page_indptr, ctx.kv_page_indices, ctx.kv_last_page_lens, hq, hkv, d, ps,
                                   data_type=torch.bfloat16, indptr_host=ctx.host["kv_page_indptr"])
             for layer in range(L):
                 pages = pool.get_layered_pages(layer)
-                dk.append_paged_kv_cache(dk_k[layer], dk_v[layer], ctx.indptr, pages, ctx.kv_page_indices,
+                main.wait_event(layer_ready[layer])
+                dk.append_paged_kv_cache(dkv[layer, 0], dkv[layer, 1], ctx.indptr, pages, ctx.kv_page_indices,
                                          ctx.kv_page_indptr, ctx.kv_last_page_lens)
                 x = wrapper.forward(x, pages)
             wrapper.end_forward()
+            step_done.record(main)
             desc_bytes[0] = 4 * (sum(len(a) for a in ctx.host.values()) + int(wrapper._plan_host[6]) + 2 * B)
             hout.copy_(x, non_blocking=True)
             for t in tasks:
@@ -540,10 +634,10 @@ def run_ours(args):
         torch.cuda.synchronize()
         e_ms = e0.elapsed_time(e1)
         result["e2e"] = {"value": e2e_steps * B / (e_ms * 1e-3), "unit": "tok/s",
-                         "h2d_bytes_per_step": int(hk.numel() * 2 * 2 + hq_host.numel() * 2 + desc_bytes[0]),
+                         "h2d_bytes_per_step": int(hkv_host.numel() * 2 + hq_host.numel() * 2 + desc_bytes[0]),
                          "d2h_bytes_per_step": int(hout.numel() * 2), "ms_per_step": e_ms / e2e_steps,
                          "api": "FlashDecodeCtx.init_paged_decode_ctx + BatchDecodeWithPagedKVCacheWrapper + "
-                                "append_paged_kv_cache, pinned host K/V/q in, pinned host out"}
+                                "append_paged_kv_cache, pinned host K/V/q in (K/V per layer on a copy stream), pinned host out"}
     if world == 1 and not args.no_prefill:
         result["prefill"] = prefill_measure(dk, args, dev)
     if do_swap:
