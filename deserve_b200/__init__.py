@@ -16,5 +16,8 @@ from .engine import (BatchDecode, BatchPrefill, BatchResult, KVStage, MicroBatch
                      StepRequest)
 from .model import LlamaStage, ModelArgs
 from .task import SamplingParams, TaskData, TaskManager
+from .request import InitRequest
+from .scheduling import DecodeFirstJoin, PrefillFirstJoin, StepPlanner, SwapPolicy, VanillaJoin
+from . import wire
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -25,6 +25,7 @@ from . import ops
 from .context import FlashDecodeCtx
 from .kvcache import PagedKVCache
 from .task import TaskData
+from .request import StepRequest  # noqa: F401  (re-exported: the stage loop's input type)
 
 
 @dataclass
@@ -343,20 +344,6 @@ class MicroBatchProcessor:
 
     def synchronize(self) -> None:
         self.kvcache_manager.synchronize()
-
-
-@dataclass
-class StepRequest:
-    """The fields of deserve_worker/request.py:137-213 that drive a stage."""
-
-    microbatch_id: int
-    xs: torch.Tensor
-    exec_task_ids: list = _field(default_factory=list)
-    exec_seqlens: list = _field(default_factory=list)
-    cancel_task_ids: list = _field(default_factory=list)
-    offload_task_ids: list = _field(default_factory=list)
-    reload_task_ids: list = _field(default_factory=list)
-    init_tasks: dict = _field(default_factory=dict)  # task id -> (prompt length, SamplingParams)
 
 
 class StageProcessor:
