@@ -589,7 +589,7 @@ def run_ours(args):
         dkv = torch.empty(L, 2, B, hkv, d, dtype=torch.bfloat16, device=dev)
         copy_stream = torch.cuda.Stream(device=dev)
         layer_ready = [torch.cuda.Event() for _ in range(L)]
-        step_done = torch.cuda.Event()
+        small_inputs_done = torch.cuda.Event()
         hq_host = torch.randn(B, hq, d).to(torch.bfloat16).pin_memory()
         hout = torch.empty(B, hq, d, dtype=torch.bfloat16).pin_memory()
         ws = torch.empty(128 << 20, dtype=torch.uint8, device=dev)
@@ -598,18 +598,22 @@ def run_ours(args):
         desc_bytes = [0]
 
         def e2e_step():
-            # Layer l's rows are uploaded on a copy stream while earlier layers compute; the compute
-            # stream waits for each layer's event, the copy stream for the previous step's last read.
+            # The step's small inputs (q, descriptors, plan) go first on the compute stream; the new K/V
+            # rows of all layers follow on a copy stream, layer by layer, while earlier layers compute. The
+            # copy stream starts behind the small inputs (else the copy engine may serve the 33 MB first and
+            # layer 0 waits for all of it) and thereby behind the previous step; the compute stream waits
+            # for each layer's event.
             main = torch.cuda.current_stream()
-            copy_stream.wait_event(step_done)
-            with torch.cuda.stream(copy_stream):
-                for layer in range(L):
-                    dkv[layer].copy_(hkv_host[layer], non_blocking=True)
-                    layer_ready[layer].record(copy_stream)
             x = hq_host.to(dev, non_blocking=True)
             ctx = dk.FlashDecodeCtx.init_paged_decode_ctx(tasks, caches, wrapper)
             wrapper.begin_forward(ctx.kv_page_indptr, ctx.kv_page_indices, ctx.kv_last_page_lens, hq, hkv, d, ps,
                                   data_type=torch.bfloat16, indptr_host=ctx.host["kv_page_indptr"])
+            small_inputs_done.record(main)
+            copy_stream.wait_event(small_inputs_done)  # which also orders it behind the previous step
+            with torch.cuda.stream(copy_stream):
+                for layer in range(L):
+                    dkv[layer].copy_(hkv_host[layer], non_blocking=True)
+                    layer_ready[layer].record(copy_stream)
             for layer in range(L):
                 pages = pool.get_layered_pages(layer)
                 main.wait_event(layer_ready[layer])
@@ -617,7 +621,6 @@ def run_ours(args):
                                          ctx.kv_page_indptr, ctx.kv_last_page_lens)
                 x = wrapper.forward(x, pages)
             wrapper.end_forward()
-            step_done.record(main)
             desc_bytes[0] = 4 * (sum(len(a) for a in ctx.host.values()) + int(wrapper._plan_host[6]) + 2 * B)
             hout.copy_(x, non_blocking=True)
             for t in tasks:
