@@ -17,6 +17,7 @@ reference's for the same inputs.
 """
 from __future__ import annotations
 
+import io
 import json
 import pickle
 import struct
@@ -79,6 +80,29 @@ def st_load(blob: bytes) -> dict[str, torch.Tensor]:
     return out
 
 
+class _MetadataUnpickler(pickle.Unpickler):
+    """Metadata is lists, dicts, strings and numbers, plus the sampling parameters of
+    prompts that start in the step. Nothing else is constructed: a frame naming any
+    other global is refused instead of imported."""
+
+    def __init__(self, data: bytes, allowed: dict):
+        super().__init__(io.BytesIO(data))
+        self._allowed = allowed
+
+    def find_class(self, module: str, name: str):
+        try:
+            return self._allowed[(module, name)]
+        except KeyError:
+            raise pickle.UnpicklingError(f"frame metadata names {module}.{name}, which is not a metadata type") from None
+
+
+def _load_metadata(data: bytes, extra_classes=()) -> dict[str, Any]:
+    from .task import SamplingParams
+
+    allowed = {(c.__module__, c.__qualname__): c for c in (SamplingParams, *extra_classes)}
+    return _MetadataUnpickler(data, allowed).load()
+
+
 def _with_standins(tensors: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
     return {(f"#{k}" if v.numel() == 0 else k): (torch.ones((1,), dtype=v.dtype) if v.numel() == 0 else v)
             for k, v in tensors.items()}
@@ -95,13 +119,14 @@ def dumps(tensors: dict[str, torch.Tensor], metadata: dict[str, Any]) -> bytes:
     return len(meta).to_bytes(4, "big") + meta + st_save(_with_standins(tensors))
 
 
-def loads(frame: bytes) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
-    """Inverse of dumps (model/utils.py:33-47). The metadata is unpickled: only
-    frames from the pipeline's own peers may be given to this function."""
+def loads(frame: bytes, extra_classes=()) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
+    """Inverse of dumps (model/utils.py:33-47). The metadata is unpickled with an
+    allow-list: plain containers and this package's SamplingParams, plus the classes
+    in `extra_classes` (inside deserve_worker: its own SamplingParams)."""
     n = int.from_bytes(frame[:4], "big")
     if 4 + n > len(frame):
         raise ValueError("frame: metadata length runs past the end")
-    return _without_standins(st_load(frame[4 + n :])), pickle.loads(frame[4 : 4 + n])
+    return _without_standins(st_load(frame[4 + n :])), _load_metadata(frame[4 : 4 + n], extra_classes)
 
 
 def dumps_network(tensors: dict[str, torch.Tensor], metadata: dict[str, Any]) -> bytes:
@@ -111,9 +136,10 @@ def dumps_network(tensors: dict[str, torch.Tensor], metadata: dict[str, Any]) ->
     return len(blob).to_bytes(4, "big") + blob + pickle.dumps(metadata)
 
 
-def loads_network(frame: bytes) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
-    """Inverse of dumps_network (server.rs:97-114, __init__.py:32-34)."""
+def loads_network(frame: bytes, extra_classes=()) -> tuple[dict[str, torch.Tensor], dict[str, Any]]:
+    """Inverse of dumps_network (server.rs:97-114, __init__.py:32-34); metadata
+    allow-list as in loads."""
     n = int.from_bytes(frame[:4], "big")
     if 4 + n > len(frame):
         raise ValueError("frame: tensor length runs past the end")
-    return st_load(frame[4 : 4 + n]), pickle.loads(frame[4 + n :])
+    return st_load(frame[4 : 4 + n]), _load_metadata(frame[4 + n :], extra_classes)

@@ -114,6 +114,24 @@ def test_wire_frame(idx):
     assert m2 == meta and torch.equal(t2["xs"], xs)
 
 
+def test_frames_carry_sampling_params_and_nothing_else():
+    import pickle
+
+    from deserve_b200.task import SamplingParams
+
+    req = StepRequest.empty(0, torch.int32)
+    req.append_exec("p", torch.arange(4, dtype=torch.int32), (4, SamplingParams(max_new_tokens=7)))
+    tensors, meta = wire.loads(wire.dumps(*req.into_safetensors()))
+    assert meta["init_tasks"]["p"][1].max_new_tokens == 7 and torch.equal(tensors["xs"], req.xs)
+    evil = pickle.dumps({"group_id": __import__("os").getcwd})  # a frame that names a callable of another module
+    frame = len(evil).to_bytes(4, "big") + evil + wire.st_save({"xs": torch.zeros(1)})
+    with pytest.raises(pickle.UnpicklingError):
+        wire.loads(frame)
+    for bad in (b"\x00\x00", b"\x00\x00\x10\x00abc"):
+        with pytest.raises(ValueError):
+            wire.loads(bad)
+
+
 def test_safetensors_container_matches_the_library():
     st = pytest.importorskip("safetensors.torch")
     g = torch.Generator().manual_seed(0)
