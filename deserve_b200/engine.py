@@ -214,6 +214,24 @@ class BatchExec:
     def total_seqlen(self) -> int:
         return sum(self.seqlens())
 
+    # Regrouping of ragged batches (exec.py:74-106): rows are stored request after request,
+    # request i owning seqlen_i of them.
+    @classmethod
+    def merge(cls, execs: Sequence["BatchExec"]) -> "BatchExec":
+        return cls(torch.cat([e.xs for e in execs]), execs[0].layer_storage,
+                   [t for e in execs for t in e.task_datas], [c for e in execs for c in e.kvcaches])
+
+    def split(self) -> list:
+        parts = self.xs.split(self.seqlens()) if self.task_datas else []
+        return [type(self)(x, self.layer_storage, [t], [c]) for x, t, c in zip(parts, self.task_datas, self.kvcaches)]
+
+    def pop(self) -> "BatchExec":
+        """Take the last request out of the batch (with its rows)."""
+        task, cache = self.task_datas.pop(), self.kvcaches.pop()
+        tail = type(self)(self.xs[-task.seqlen:], self.layer_storage, [task], [cache])
+        self.xs = self.xs[: -task.seqlen]
+        return tail
+
     def post_process(self, result: torch.Tensor, ignore_eos: bool) -> BatchResult:
         ids = [t.task_id for t in self.task_datas]
         if not self.layer_storage.need_sample:

@@ -156,3 +156,21 @@ def test_step_planner_budget_and_chunking():
     assert req.init_tasks["p0"][0] == 100 and not planner.pending_prompts
     with pytest.raises(ValueError):
         StepPlanner(manager, 1, policy="nope")
+
+
+def test_batch_exec_regrouping():
+    from deserve_b200.engine import BatchDecode, BatchExec, BatchPrefill
+
+    sp = SamplingParams()
+    tasks = [TaskData(f"t{i}", 0, 0, n, n, sp) for i, n in enumerate([3, 1, 4])]
+    xs = torch.arange(8 * 2).reshape(8, 2)
+    batch = BatchPrefill(xs, "storage", list(tasks), ["c0", "c1", "c2"])
+    assert batch.bsz() == 3 and batch.seqlens() == [3, 1, 4] and batch.total_seqlen() == 8
+    parts = batch.split()
+    assert [p.xs.shape[0] for p in parts] == [3, 1, 4] and all(isinstance(p, BatchPrefill) for p in parts)
+    assert torch.equal(parts[2].xs, xs[4:]) and parts[1].kvcaches == ["c1"]
+    again = BatchPrefill.merge(parts)
+    assert isinstance(again, BatchPrefill) and torch.equal(again.xs, xs) and again.task_datas == tasks
+    last = batch.pop()
+    assert last.task_datas == [tasks[2]] and torch.equal(last.xs, xs[4:]) and batch.xs.shape[0] == 4 and batch.bsz() == 2
+    assert isinstance(BatchDecode.merge([BatchExec(xs[:1], "s", tasks[1:2], ["c1"])]), BatchDecode)
