@@ -61,6 +61,10 @@ def parse_args():
     ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (16 GiB of scattered pages out and back)")
     ap.add_argument("--swap-seqs", type=int, default=64)
     ap.add_argument("--swap-tokens", type=int, default=2048)
+    ap.add_argument("--hop", default="auto", choices=["auto", "peer", "nccl"],
+                    help="N > 1: how a stage hands its activations on. peer = the sender's kernel stores into the "
+                         "next GPU's inbox over NVLink (deserve_b200.peer); nccl = grouped send/recv; auto = peer, "
+                         "and nccl if peer memory cannot be set up")
     ap.add_argument("--compare-library", action="store_true",
                     help="only time flashinfer (the library the reference calls) and this package on the same "
                          "one-layer decode and chunked-prefill inputs; prints its own JSON line")
@@ -453,6 +457,7 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only
         dist.init_process_group("nccl", device_id=dev)
     if args.layers % world:
         raise SystemExit("--layers must be divisible by --gpus")
@@ -509,7 +514,25 @@ def run_ours(args):
         launches[0] += L * (2 + (1 if descs[(m, s)].workspace_bytes > 0 else 0))
         return stage.forward(x, k_new[m], v_new[m], descs[(m, s)])
 
-    pipe = RingPipeline(rank, world, stage_fn, lambda m: q0[m], total_steps, dist=dist)
+    peer_hop, hop_name = None, "none"
+    if world > 1:
+        hop_name = "nccl send/recv"
+        if args.hop in ("auto", "peer"):
+            ok = torch.ones(1, device=dev)
+            try:
+                from deserve_b200.peer import PeerHop
+                peer_hop = PeerHop(rank, world, (B, hq, d), torch.bfloat16, dev, dist.group.WORLD)
+            except Exception as exc:  # no peer mapping on this node: every rank must take the same path
+                if args.hop == "peer":
+                    raise
+                print(f"[bench] rank {rank}: peer memory hop unavailable ({exc!r})", file=sys.stderr, flush=True)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                peer_hop = None
+            else:
+                hop_name = "peer-memory stores + flags"
+    pipe = RingPipeline(rank, world, stage_fn, lambda m: q0[m], total_steps, dist=dist, peer_hop=peer_hop)
 
     def barrier():
         if world > 1:
@@ -520,6 +543,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier()
     launches[0] = 0
+    hop_launches0 = peer_hop.launches if peer_hop is not None else 0
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         torch.cuda.synchronize()
@@ -536,12 +560,12 @@ def run_ours(args):
         pipe.advance(world - 1)  # drain so that every rank leaves with matching send/recv counts
     tokens = K * M * B
     value = tokens / (ms * 1e-3)
-    timed_launches = launches[0]
+    timed_launches = launches[0] + ((peer_hop.launches - hop_launches0) if peer_hop is not None else 0)
 
     result = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": Wm,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": config_dict(args, world), "gpu_launches": timed_launches,
+        "data": "synthetic", "config": dict(config_dict(args, world), hop=hop_name), "gpu_launches": timed_launches,
         "clocks": clocks.summary(),
     }
 

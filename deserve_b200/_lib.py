@@ -51,6 +51,9 @@ _SIGNATURES = {
     "dsv_device_info": (c_int, [POINTER(c_int)] * 3),
     "dsv_read_device_status": (c_int, [POINTER(c_int)]),
     "dsv_selftest_wait_timeout": (c_int, [c_int, c_void_p]),
+    "dsv_peer_push": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int, c_void_p]),
+    "dsv_peer_signal": (c_int, [c_void_p, c_int32, c_void_p]),
+    "dsv_peer_wait": (c_int, [c_void_p, c_int32, c_int64, c_void_p]),
     "dsv_host_build_step": (c_int, [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                     c_int32, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),

@@ -103,10 +103,12 @@ class RingPipeline:
     """
 
     def __init__(self, rank: int, world: int, stage_fn, first_input, total_steps: int, group=None, dist=None,
-                 recv_spec=None):
+                 recv_spec=None, peer_hop=None):
         # recv_spec(unit) -> (shape, dtype, device) of the tensor this rank consumes as input of `unit`;
         # None: same shape as what it sends
         self.recv_spec = recv_spec
+        # peer_hop (deserve_b200.peer.PeerHop): messages go through peer memory instead of NCCL send/recv
+        self.peer_hop = peer_hop
         self.rank, self.world = rank, world
         self.stage_fn, self.first_input = stage_fn, first_input
         self.units = total_steps * world
@@ -128,12 +130,19 @@ class RingPipeline:
             if self._computes(r, t):
                 u = t - r
                 m, s = u % W, u // W
-                x = self.first_input(m) if (r == 0 and s == 0) else self.inbox
+                from_peer = self.peer_hop is not None and not (r == 0 and s == 0)
+                x = self.first_input(m) if (r == 0 and s == 0) else (self.peer_hop.recv() if from_peer else self.inbox)
                 y = self.stage_fn(u, m, s, x)
+                if from_peer:
+                    self.peer_hop.release()
                 if r == W - 1:
                     self.completed.append((m, s))
                     self.last_output = y
-            if W > 1:
+            if W > 1 and self.peer_hop is not None:
+                # same send condition as below; the matching receive happens where the message is used
+                if y is not None and (r < W - 1 or t + 1 < self.units):
+                    self.peer_hop.send(y)
+            elif W > 1:
                 nxt, prv = (r + 1) % W, (r - 1) % W
                 # what rank r+1 computes in slot t+1 is the unit rank r computed in slot t;
                 # rank 0 needs the last rank's output only while token steps remain

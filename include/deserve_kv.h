@@ -332,6 +332,29 @@ int dsv_host_build_step(uint8_t* bitmap, int32_t num_pages, int32_t* buffer, int
                         int32_t* failed_need);
 
 /*
+ * The hop between pipeline stages over peer memory. The reference posts each
+ * microbatch's activations to the next worker over HTTP
+ * (deserve_worker/engine/pipeline/processor.py:218-224, PipelineProcessor.send_request);
+ * on one NVLink node the sender stores them into the next GPU's inbox instead.
+ *   dsv_peer_push   copies `bytes` (multiple of 16) from src (local) to dst (a
+ *                   peer-mapped or local device address) with plain 16-byte stores and,
+ *                   when every store is visible system-wide, writes `value` to *flag
+ *                   (normally in the receiver's memory). `arrivals`: one uint32 of local
+ *                   device scratch, zero before the first call (it returns to zero).
+ *   dsv_peer_signal writes `value` to *flag after a system-wide fence (credits going back
+ *                   to the sender).
+ *   dsv_peer_wait   holds the stream until *flag >= value: one thread polls with
+ *                   acquire loads, at most max_polls times; on expiry the kernel ends,
+ *                   the device status reads 4 (wait timeout) and the stream continues.
+ * Flags are int32 that only grow (message number + 1). No TMA, no multicast: peer
+ * memory is written with ordinary stores only.
+ */
+int dsv_peer_push(void* dst, const void* src, int64_t bytes, int32_t* flag, int32_t value,
+                  uint32_t* arrivals, int sm_count, void* stream);
+int dsv_peer_signal(int32_t* flag, int32_t value, void* stream);
+int dsv_peer_wait(const int32_t* flag, int32_t value, int64_t max_polls, void* stream);
+
+/*
  * Self-test of the bounded waits every mbarrier-based kernel here uses: launches
  * one thread that polls (at most `polls` times) a barrier phase nothing will
  * ever complete. The wait gives up, the kernel ends normally and
