@@ -33,6 +33,35 @@ def _expected(world, steps):
     return out
 
 
+class _GlooHop:
+    """Stands in for deserve_b200.peer.PeerHop on CPU: same three calls, gloo underneath. It checks
+    the protocol the ring must follow: every message sent is received once, in order, and released."""
+
+    def __init__(self, dist, rank, world):
+        self.dist, self.nxt, self.prv = dist, (rank + 1) % world, (rank - 1) % world
+        self.sent = self.received = self.released = 0
+        self._pending = []
+
+    def send(self, y):
+        self._pending.append(self.dist.isend(torch.cat([torch.tensor([float(self.sent)]), y.flatten()]), self.nxt))
+        self.sent += 1
+
+    def recv(self):
+        assert self.received == self.released, "recv() before the previous message was released"
+        buf = torch.empty(1 + 12)
+        self.dist.recv(buf, self.prv)
+        assert int(buf[0]) == self.received, "messages out of order"
+        self.received += 1
+        return buf[1:].reshape(4, 3).clone()
+
+    def release(self):
+        self.released += 1
+
+    def close(self):
+        for w in self._pending:
+            w.wait()
+
+
 def _worker(rank, world, port, steps, split, q):
     sys.path.insert(0, str(ROOT))
     import torch.distributed as dist
@@ -47,7 +76,9 @@ def _worker(rank, world, port, steps, split, q):
         seen.append((m, s))
         return _stage_math(rank, m, s, x)
 
-    pipe = RingPipeline(rank, world, stage_fn, lambda m: torch.full((4, 3), float(m)), steps, dist=dist)
+    hop = _GlooHop(dist, rank, world) if split == "hop" else None
+    split = [] if split == "hop" else split
+    pipe = RingPipeline(rank, world, stage_fn, lambda m: torch.full((4, 3), float(m)), steps, dist=dist, peer_hop=hop)
     finals = {}
     total_slots = steps * world + world - 1
     done = 0
@@ -60,11 +91,16 @@ def _worker(rank, world, port, steps, split, q):
                 before = len(pipe.completed)
         done += n
         dist.barrier()
+    if hop is not None:
+        hop.close()
+        # rank 0 takes its first `world` inputs from first_input, everything else arrives over the hop
+        assert hop.received == hop.released == steps * world - (world if rank == 0 else 0)
+        assert hop.sent == steps * world - (world if rank == world - 1 else 0)
     q.put((rank, seen, {k: v.tolist() for k, v in finals.items()}))
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,steps,split", [(2, 3, [2]), (3, 2, [3, 1]), (2, 1, [])])
+@pytest.mark.parametrize("world,steps,split", [(2, 3, [2]), (3, 2, [3, 1]), (2, 1, []), (3, 3, "hop"), (4, 2, "hop")])
 def test_ring_pipeline_matches_sequential(world, steps, split):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
