@@ -61,7 +61,7 @@ def parse_args():
     ap.add_argument("--no-swap", action="store_true", help="skip the KV swap stress (16 GiB of scattered pages out and back)")
     ap.add_argument("--swap-seqs", type=int, default=64)
     ap.add_argument("--swap-tokens", type=int, default=2048)
-    ap.add_argument("--hop", default="auto", choices=["auto", "peer", "nccl"],
+    ap.add_argument("--hop", default="nccl", choices=["auto", "peer", "nccl"],
                     help="N > 1: how a stage hands its activations on. peer = the sender's kernel stores into the "
                          "next GPU's inbox over NVLink (deserve_b200.peer); nccl = grouped send/recv; auto = peer, "
                          "and nccl if peer memory cannot be set up")
