@@ -204,3 +204,51 @@ def test_kernels_refuse_cpu_tensors():
         dk.append_paged_kv_cache(k, k, i32, pages, i32, i32, i32[:1])
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         dk.apply_rope(k, k, i32, i32[:1])
+
+
+@pytest.mark.parametrize("native", [False, True])
+@pytest.mark.parametrize("seed", range(6))
+def test_allocator_agrees_with_oracle_on_random_histories(seed, native):
+    """Differential check beyond the recorded traces: random create / grow / free
+    histories (pool exhaustion included) through the product's classes, grown either by
+    the Python classes or by the native step builder, against the CPU oracle that the
+    reference traces pin."""
+    import random
+
+    from oracle.paged_alloc import OracleKVCache, OraclePagePool, OraclePageTables
+
+    rng = random.Random(1000 + seed)
+    ps = rng.choice([4, 8, 16])
+    num_pages, max_req = rng.choice([40, 90, 200]), rng.choice([4, 9, 16])
+    pool = dk.CpuPagePool(1, num_pages, ps, torch.float16, n_kv_heads=1, head_dim=8)
+    pta = dk.PageTableAllocator(max_req, 4096, ps, CPU)
+    opool, otab = OraclePagePool(num_pages, ps), OraclePageTables(max_req, 4096, ps)
+    live = {}
+    for step in range(300):
+        r = rng.random()
+        if (r < 0.25 or not live) and len(live) < max_req:
+            live[step] = [dk.PagedKVCache.empty(pta, pool), OracleKVCache(otab, opool), 0]
+            assert live[step][0].page_table.offset == live[step][1].slot
+        elif r < 0.8:
+            cid = rng.choice(list(live))
+            mine, theirs, tokens = live[cid]
+            tokens += rng.choice([1, 1, 1, 2, ps, ps + 1, 5 * ps, 23 * ps])
+            try:
+                theirs.extend(tokens)
+                ok = True
+            except ValueError:
+                ok = False
+            if ok:
+                assert _extend(mine, tokens, native) is True
+                live[cid][2] = tokens
+                assert mine.page_table.retrieve().tolist() == theirs.page_ids().tolist()
+            else:
+                with pytest.raises(ValueError, match="Not enough pages"):
+                    _extend(mine, tokens, native)
+        else:
+            mine, theirs, _ = live.pop(rng.choice(list(live)))
+            mine.free()
+            theirs.free()
+        assert pool.num_avails == opool.num_avails
+        assert pool.page_buffer.tolist() == opool.buffer.tolist()
+        assert pool.page_bitmap.numpy().tolist() == opool.bitmap.tolist()
