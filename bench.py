@@ -65,6 +65,9 @@ def parse_args():
                     help="N > 1: how a stage hands its activations on. peer = the sender's kernel stores into the "
                          "next GPU's inbox over NVLink (deserve_b200.peer); nccl = grouped send/recv; auto = peer, "
                          "and nccl if peer memory cannot be set up")
+    ap.add_argument("--measure-hop", action="store_true",
+                    help="N > 1 only: time one 2 MiB hop around the ring, NCCL send/recv against the peer-memory "
+                         "transport, with nothing else on the GPUs; prints its own JSON line")
     ap.add_argument("--compare-library", action="store_true",
                     help="only time flashinfer (the library the reference calls) and this package on the same "
                          "one-layer decode and chunked-prefill inputs; prints its own JSON line")
@@ -369,6 +372,50 @@ def library_compare(dk, args, dev, iters=20):
     return out
 
 
+def measure_hop(args, rank, world, dev, dist, iters=200):
+    """Every rank sends [batch, q_heads, head_dim] bf16 to its successor and receives from its predecessor,
+    `iters` times back to back, once with a grouped NCCL send/recv and once through deserve_b200.peer.PeerHop.
+    Device time per hop, max over ranks."""
+    from deserve_b200.peer import PeerHop
+
+    shape = (args.batch, args.q_heads, args.head_dim)
+    y = torch.randn(shape, device=dev).to(torch.bfloat16)
+    buf = torch.empty_like(y)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+
+    def nccl_hop():
+        for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, y, nxt), dist.P2POp(dist.irecv, buf, prv)]):
+            w.wait()
+
+    hop = PeerHop(rank, world, shape, torch.bfloat16, dev, dist.group.WORLD)
+
+    def peer_hop():
+        hop.send(y)
+        got = hop.recv()
+        buf.copy_(got)  # a consumer kernel, as the first layer's attention would be
+        hop.release()
+
+    out = {}
+    for name, fn in (("nccl", nccl_hop), ("peer", peer_hop)):
+        for _ in range(10):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[f"{name}_us_per_hop"] = float(t.item())
+    hop.close()
+    out["bytes"] = y.numel() * 2
+    out["n_gpus"] = world
+    return out
+
+
 def swap_stress(dk, pool, free_ids, args, dev, decode_step):
     """KV swap stress: the KV of swap_seqs x swap_tokens tokens, all layers, scattered over the
     permuted pool, is swapped out to pinned host chunks and back into DIFFERENT pages while decode
@@ -459,6 +506,15 @@ def run_ours(args):
     if world > 1:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only
         dist.init_process_group("nccl", device_id=dev)
+    if args.measure_hop:
+        if world < 2:
+            raise SystemExit("--measure-hop needs --gpus 2 or more")
+        res = measure_hop(args, rank, world, dev, dist)
+        if rank == 0:
+            print(json.dumps({"hop": res}), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     if args.layers % world:
         raise SystemExit("--layers must be divisible by --gpus")
     L = args.layers // world
