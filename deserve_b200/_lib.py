@@ -79,14 +79,14 @@ _SIGNATURES = {
     "dsv_paged_prefill": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_float, c_int, c_void_p]),
-    "dsv_pack_pages": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
-                               c_void_p]),
-    "dsv_unpack_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int,
-                                 c_int, c_void_p]),
-    "dsv_swap_out_pages": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                   c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "dsv_swap_in_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "dsv_pack_pages": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
+                               c_void_p, c_void_p]),
+    "dsv_unpack_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64,
+                                 c_int, c_int, c_void_p]),
+    "dsv_swap_out_pages": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "dsv_swap_in_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "dsv_region_swap": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p]),
 }

@@ -6,6 +6,7 @@ Python package loads. nvcc cross-compiles without a GPU.
 """
 from __future__ import annotations
 
+import fcntl
 import os
 import shutil
 import subprocess
@@ -45,12 +46,26 @@ def is_stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every .cu under csrc/ into one shared library; return its path."""
+    """Compile every .cu under csrc/ into one shared library; return its path.
+    Processes that arrive together (the ranks of a multi-GPU launch importing the
+    package at the same time) take turns on a lock file: the first one compiles,
+    the others find the library fresh when their turn comes."""
     if not force and not is_stale():
         return LIB_PATH
-    nvcc = _nvcc()
     objdir = PKG_DIR / "build"
     objdir.mkdir(exist_ok=True)
+    with open(objdir / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale():
+                return LIB_PATH
+            return _build_locked(objdir, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(objdir: Path, verbose: bool) -> Path:
+    nvcc = _nvcc()
     procs = []
     objs = []
     for src in sources():

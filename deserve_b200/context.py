@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from .pinned import ring as _pinned_ring
 from .kvcache import PagedKVCache, PagePool
 from .task import TaskData
 
@@ -95,9 +96,16 @@ class FlashForwardCtx(PagedForwardCtx):
         bsz = len(task_datas)
         ps = pool.page_size
         cap = 5 * (bsz + 4) + sum((t.start_pos + t.seqlen + ps - 1) // ps for t in task_datas) + 4
-        pinned = torch.empty(cap, dtype=torch.int32, pin_memory=on_gpu)
+        if on_gpu:
+            pinned, slot = _pinned_ring("descriptors", slots=16).take(cap)
+        else:
+            pinned = torch.empty(cap, dtype=torch.int32)
         _, used, host = build_step(task_datas, kvcaches, pinned.numpy())
-        dev = pinned[:used].to(pool.main_device, non_blocking=True) if on_gpu else pinned
+        if on_gpu:
+            dev = pinned[:used].to(pool.main_device, non_blocking=True)
+            _pinned_ring("descriptors").done(slot)
+        else:
+            dev = pinned
         starts = {n: host[n].ctypes.data - pinned.data_ptr() for n in _NAMES}
         t = {n: dev[starts[n] // 4 : starts[n] // 4 + len(host[n])] for n in _NAMES}
         ctx = FlashForwardCtx(

@@ -12,6 +12,7 @@
 // the 8 lanes with warp shuffles, the online softmax state (m, l, o) is kept
 // per lane group in fp32 and merged by shuffles at the end of the item.
 #include <algorithm>
+#include <mutex>
 #include <cmath>
 #include <vector>
 
@@ -679,12 +680,15 @@ static __device__ __align__(256) unsigned char g_decode_scratch[DSV_STATIC_SCRAT
 namespace {
 constexpr int kMaxScratchDevices = 64;
 void* g_scratch_ptr[kMaxScratchDevices] = {nullptr};
+std::mutex g_scratch_mutex;
 
-// Device address of g_decode_scratch on the current device, resolved once per device.
+// Device address of g_decode_scratch on the current device, resolved once per device
+// (under a lock: two host threads may make their first call on a device at the same time).
 int static_scratch(void** out) {
   int dev = -1;
   DSV_CUDA(cudaGetDevice(&dev));
   DSV_REQUIRE(dev >= 0 && dev < kMaxScratchDevices, "decode_static: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (g_scratch_ptr[dev] == nullptr) {
     void* ptr = nullptr;
     DSV_CUDA(cudaGetSymbolAddress(&ptr, g_decode_scratch));

@@ -17,7 +17,7 @@ constexpr int kCopyThreads = 256;
 // A CTA copies whole rows: 16 bytes per thread per trip, 4 trips in flight.
 template <bool kPack>
 __global__ void __launch_bounds__(kCopyThreads)
-pack_kernel(unsigned char* __restrict__ pages_base, int64_t layer_stride_bytes, int page_vecs,
+pack_kernel(unsigned char* __restrict__ pages_base, int64_t layer_stride_bytes, int page_vecs, int64_t num_pages,
             const int32_t* __restrict__ page_ids, const int32_t* __restrict__ ids_indptr, int n_tasks,
             int64_t total_rows, int layer_begin, int window, unsigned char* __restrict__ packed,
             int* status) {
@@ -36,7 +36,7 @@ pack_kernel(unsigned char* __restrict__ pages_base, int64_t layer_stride_bytes, 
     }
     const int layer = layer_begin + (int)(local / n_t);
     const int page = __ldg(page_ids + i0 + (int)(local % n_t));
-    if (page < 0) {
+    if (page < 0 || page >= num_pages) {  // a stale id must never reach memory outside the slab
       if (threadIdx.x == 0) record_status(status, ST_BAD_PAGE_ID);
       continue;
     }
@@ -62,7 +62,7 @@ pack_kernel(unsigned char* __restrict__ pages_base, int64_t layer_stride_bytes, 
 
 // returns <0 error, 1 nothing to do, 0 go
 int check_pack_args(const char* who, const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
-                    const int32_t* page_ids, const int32_t* ids_indptr, int n_tasks, int64_t total_ids,
+                    int64_t num_pages, const int32_t* page_ids, const int32_t* ids_indptr, int n_tasks, int64_t total_ids,
                     int layer_begin, int layer_end, const void* packed) {
   DSV_REQUIRE(n_tasks >= 0 && total_ids >= 0, "%s: negative task or page count", who);
   if (n_tasks == 0 || total_ids == 0) return 1;
@@ -70,7 +70,11 @@ int check_pack_args(const char* who, const void* pages_base, int64_t layer_strid
   DSV_REQUIRE(page_bytes > 0 && page_bytes % 16 == 0, "%s: page_bytes (%lld) must be a positive multiple of 16", who,
               (long long)page_bytes);
   DSV_REQUIRE(page_bytes / 16 < (1ll << 31), "%s: page too large", who);
-  DSV_REQUIRE(layer_stride_bytes % 16 == 0 && layer_stride_bytes >= page_bytes, "%s: bad layer stride", who);
+  DSV_REQUIRE(num_pages > 0 && num_pages < (1ll << 31), "%s: num_pages (%lld) out of range", who,
+              (long long)num_pages);
+  DSV_REQUIRE(layer_stride_bytes % 16 == 0 && layer_stride_bytes >= num_pages * page_bytes,
+              "%s: a layer slab of %lld bytes cannot hold %lld pages of %lld bytes", who,
+              (long long)layer_stride_bytes, (long long)num_pages, (long long)page_bytes);
   DSV_REQUIRE(layer_begin >= 0 && layer_end > layer_begin, "%s: empty layer window [%d,%d)", who, layer_begin,
               layer_end);
   DSV_REQUIRE(aligned16(pages_base) && aligned16(packed), "%s: pointers must be 16-byte aligned", who);
@@ -78,15 +82,16 @@ int check_pack_args(const char* who, const void* pages_base, int64_t layer_strid
 }
 
 template <bool kPack>
-int launch_pack(unsigned char* pages_base, int64_t layer_stride_bytes, int64_t page_bytes, const int32_t* page_ids,
+int launch_pack(unsigned char* pages_base, int64_t layer_stride_bytes, int64_t page_bytes, int64_t num_pages,
+                const int32_t* page_ids,
                 const int32_t* ids_indptr, int n_tasks, int64_t total_ids, int layer_begin, int layer_end,
                 unsigned char* packed, cudaStream_t st) {
   const int window = layer_end - layer_begin;
   const int64_t total_rows = total_ids * window;
   // enough CTAs to cover the machine several times over; further rows are strided
   const unsigned grid = (unsigned)std::min<int64_t>(total_rows, 148 * 16);
-  pack_kernel<kPack><<<grid, kCopyThreads, 0, st>>>(pages_base, layer_stride_bytes, (int)(page_bytes / 16), page_ids,
-                                                    ids_indptr, n_tasks, total_rows, layer_begin, window, packed,
+  pack_kernel<kPack><<<grid, kCopyThreads, 0, st>>>(pages_base, layer_stride_bytes, (int)(page_bytes / 16), num_pages,
+                                                    page_ids, ids_indptr, n_tasks, total_rows, layer_begin, window, packed,
                                                     device_status_ptr());
   DSV_CUDA(cudaGetLastError());
   return DSV_OK;
@@ -94,7 +99,7 @@ int launch_pack(unsigned char* pages_base, int64_t layer_stride_bytes, int64_t p
 
 struct SwapArgs {
   unsigned char* pages_base;
-  int64_t layer_stride_bytes, page_bytes;
+  int64_t layer_stride_bytes, page_bytes, num_pages;
   int num_layers;
   const int32_t *page_ids, *ids_indptr, *ids_indptr_host;
   const int64_t* chunk_row_begin_host;
@@ -117,7 +122,8 @@ int check_swap_args(const char* who, const SwapArgs& a, int64_t* total_ids, int*
                 "%s: bad task descriptor %d", who, t);
   *total_ids = a.ids_indptr_host[a.n_tasks];
   if (*total_ids == 0) return 1;
-  const int rc = check_pack_args(who, a.pages_base, a.layer_stride_bytes, a.page_bytes, a.page_ids, a.ids_indptr,
+  const int rc = check_pack_args(who, a.pages_base, a.layer_stride_bytes, a.page_bytes, a.num_pages, a.page_ids,
+                                 a.ids_indptr,
                                  a.n_tasks, *total_ids, 0, a.num_layers, a.staging);
   if (rc != 0) return rc;
   for (int i = 0; i < 4; ++i) DSV_REQUIRE(a.ev[i] != nullptr, "%s: null event %d", who, i);
@@ -135,35 +141,35 @@ int check_swap_args(const char* who, const SwapArgs& a, int64_t* total_ids, int*
 
 extern "C" {
 
-int dsv_pack_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
+int dsv_pack_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes, int64_t num_pages,
                    const int32_t* page_ids, const int32_t* ids_indptr, int n_tasks,
                    int64_t total_ids, int layer_begin, int layer_end, void* dst, void* stream) {
   using namespace dsv;
-  const int rc = check_pack_args("pack_pages", pages_base, layer_stride_bytes, page_bytes, page_ids, ids_indptr,
+  const int rc = check_pack_args("pack_pages", pages_base, layer_stride_bytes, page_bytes, num_pages, page_ids, ids_indptr,
                                  n_tasks, total_ids, layer_begin, layer_end, dst);
   if (rc != 0) return rc < 0 ? rc : DSV_OK;
-  return launch_pack<true>((unsigned char*)pages_base, layer_stride_bytes, page_bytes, page_ids, ids_indptr, n_tasks,
+  return launch_pack<true>((unsigned char*)pages_base, layer_stride_bytes, page_bytes, num_pages, page_ids, ids_indptr, n_tasks,
                            total_ids, layer_begin, layer_end, (unsigned char*)dst, (cudaStream_t)stream);
 }
 
 int dsv_unpack_pages(const void* src, void* pages_base, int64_t layer_stride_bytes,
-                     int64_t page_bytes, const int32_t* page_ids, const int32_t* ids_indptr,
+                     int64_t page_bytes, int64_t num_pages, const int32_t* page_ids, const int32_t* ids_indptr,
                      int n_tasks, int64_t total_ids, int layer_begin, int layer_end, void* stream) {
   using namespace dsv;
-  const int rc = check_pack_args("unpack_pages", pages_base, layer_stride_bytes, page_bytes, page_ids, ids_indptr,
+  const int rc = check_pack_args("unpack_pages", pages_base, layer_stride_bytes, page_bytes, num_pages, page_ids, ids_indptr,
                                  n_tasks, total_ids, layer_begin, layer_end, src);
   if (rc != 0) return rc < 0 ? rc : DSV_OK;
-  return launch_pack<false>((unsigned char*)pages_base, layer_stride_bytes, page_bytes, page_ids, ids_indptr, n_tasks,
+  return launch_pack<false>((unsigned char*)pages_base, layer_stride_bytes, page_bytes, num_pages, page_ids, ids_indptr, n_tasks,
                             total_ids, layer_begin, layer_end, (unsigned char*)src, (cudaStream_t)stream);
 }
 
 int dsv_swap_out_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
-                       int num_layers, const int32_t* page_ids, const int32_t* ids_indptr,
+                       int64_t num_pages, int num_layers, const int32_t* page_ids, const int32_t* ids_indptr,
                        const int32_t* ids_indptr_host, const int64_t* chunk_row_begin_host,
                        int n_tasks, void* staging, int64_t staging_bytes, void* host_pool,
                        void* stream_kernel, void* stream_dma, void** events) {
   using namespace dsv;
-  SwapArgs a{(unsigned char*)pages_base, layer_stride_bytes, page_bytes, num_layers, page_ids, ids_indptr,
+  SwapArgs a{(unsigned char*)pages_base, layer_stride_bytes, page_bytes, num_pages, num_layers, page_ids, ids_indptr,
              ids_indptr_host, chunk_row_begin_host, n_tasks, (unsigned char*)staging, staging_bytes,
              (unsigned char*)host_pool, (cudaStream_t)stream_kernel, (cudaStream_t)stream_dma, (cudaEvent_t*)events};
   int64_t total_ids = 0;
@@ -175,9 +181,12 @@ int dsv_swap_out_pages(const void* pages_base, int64_t layer_stride_bytes, int64
   for (int l0 = 0; l0 < num_layers; l0 += window, ++w) {
     const int l1 = std::min(num_layers, l0 + window), h = w & 1;
     unsigned char* buf = a.staging + h * half;
-    // the DMA that last read this half must be done before it is refilled
-    if (w >= 2) DSV_CUDA(cudaStreamWaitEvent(a.s_kernel, a.ev[2 + h], 0));
-    const int prc = launch_pack<true>(a.pages_base, layer_stride_bytes, page_bytes, page_ids, ids_indptr, n_tasks,
+    // The DMA that last read this half must be done before it is refilled. That DMA may belong
+    // to an EARLIER call that shares the staging buffer and the events (back-to-back offloads
+    // with no host wait in between), so the edge is taken for every window, the first two
+    // included; on a fresh event it is a no-op.
+    DSV_CUDA(cudaStreamWaitEvent(a.s_kernel, a.ev[2 + h], 0));
+    const int prc = launch_pack<true>(a.pages_base, layer_stride_bytes, page_bytes, num_pages, page_ids, ids_indptr, n_tasks,
                                       total_ids, l0, l1, buf, a.s_kernel);
     if (prc != DSV_OK) return prc;
     DSV_CUDA(cudaEventRecord(a.ev[h], a.s_kernel));
@@ -196,13 +205,13 @@ int dsv_swap_out_pages(const void* pages_base, int64_t layer_stride_bytes, int64
 }
 
 int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_stride_bytes,
-                      int64_t page_bytes, int num_layers, const int32_t* page_ids,
+                      int64_t page_bytes, int64_t num_pages, int num_layers, const int32_t* page_ids,
                       const int32_t* ids_indptr, const int32_t* ids_indptr_host,
                       const int64_t* chunk_row_begin_host, int n_tasks, void* staging,
                       int64_t staging_bytes, void* stream_kernel, void* stream_dma,
                       void** events) {
   using namespace dsv;
-  SwapArgs a{(unsigned char*)pages_base, layer_stride_bytes, page_bytes, num_layers, page_ids, ids_indptr,
+  SwapArgs a{(unsigned char*)pages_base, layer_stride_bytes, page_bytes, num_pages, num_layers, page_ids, ids_indptr,
              ids_indptr_host, chunk_row_begin_host, n_tasks, (unsigned char*)staging, staging_bytes,
              (unsigned char*)host_pool, (cudaStream_t)stream_kernel, (cudaStream_t)stream_dma, (cudaEvent_t*)events};
   int64_t total_ids = 0;
@@ -214,8 +223,9 @@ int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_str
   for (int l0 = 0; l0 < num_layers; l0 += window, ++w) {
     const int l1 = std::min(num_layers, l0 + window), h = w & 1;
     unsigned char* buf = a.staging + h * half;
-    // the unpack that last read this half must be done before it is overwritten
-    if (w >= 2) DSV_CUDA(cudaStreamWaitEvent(a.s_dma, a.ev[2 + h], 0));
+    // The unpack that last read this half must be done before it is overwritten; as above, it may
+    // be an earlier call's, so every window takes the edge.
+    DSV_CUDA(cudaStreamWaitEvent(a.s_dma, a.ev[2 + h], 0));
     for (int t = 0; t < n_tasks; ++t) {
       const int64_t n_t = ids_indptr_host[t + 1] - ids_indptr_host[t];
       if (n_t == 0) continue;
@@ -226,7 +236,7 @@ int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_str
     }
     DSV_CUDA(cudaEventRecord(a.ev[h], a.s_dma));
     DSV_CUDA(cudaStreamWaitEvent(a.s_kernel, a.ev[h], 0));
-    const int prc = launch_pack<false>(a.pages_base, layer_stride_bytes, page_bytes, page_ids, ids_indptr, n_tasks,
+    const int prc = launch_pack<false>(a.pages_base, layer_stride_bytes, page_bytes, num_pages, page_ids, ids_indptr, n_tasks,
                                        total_ids, l0, l1, buf, a.s_kernel);
     if (prc != DSV_OK) return prc;
     DSV_CUDA(cudaEventRecord(a.ev[2 + h], a.s_kernel));

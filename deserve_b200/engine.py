@@ -48,7 +48,7 @@ def prepare_decode_step(task_datas: Sequence[TaskData], kvcaches: Sequence[Paged
     (one H2D copy) and the split-KV plan (one more)."""
     ctx = FlashDecodeCtx.init_paged_decode_ctx(list(task_datas), list(kvcaches), None)
     pool = ctx.page_pool
-    plan = torch.empty(ops.plan_capacity(ctx.bsz, sm_count), dtype=torch.int32, pin_memory=True)
+    plan = torch.empty(ops.plan_capacity(ctx.bsz, sm_count), dtype=torch.int32, pin_memory=True)  # kept by the caller
     used, ws = ops.make_decode_plan(ctx.host["kv_page_indptr"], n_q_heads, pool.n_kv_heads, pool.head_dim,
                                     pool.page_size, pool.main_dtype, sm_count, plan.numpy())
     plan_dev = plan[:used].to(pool.main_device, non_blocking=True)

@@ -27,6 +27,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from .pinned import ring as _pinned_ring
 
 
 def _as_ids(x) -> np.ndarray:
@@ -136,6 +137,22 @@ class PagePool:
         """`size` page ids as an int32 tensor (host memory). Raises ValueError
         when the pool cannot satisfy the request."""
         return torch.from_numpy(self._alloc_np(size))
+
+    def reserve(self, ids) -> None:
+        """Take the given page ids out of the free set (they must all be free and not
+        in the prefetch buffer): for callers that place a cache on pages of their own
+        choosing, e.g. a seeded random permutation of the pool, and hand the ids to
+        PageTableHandle.extend themselves. free() returns them as usual."""
+        ids = _as_ids(ids)
+        with self.mutex:
+            if len(ids) == 0:
+                return
+            if ids.min() < 0 or ids.max() >= self.num_pages:
+                raise ValueError("reserve: page id outside the pool")
+            if len(np.unique(ids)) != len(ids) or not self._bitmap[ids].all():
+                raise ValueError("reserve: a page is not free (or is listed twice)")
+            self._bitmap[ids] = False
+            self.num_avails -= len(ids)
 
     def alloc_consecutive(self, size: int) -> Optional[torch.Tensor]:
         """First run of `size` consecutive free pages, or None."""
@@ -565,15 +582,21 @@ class KVCacheManager:
     def _ensure_staging(self, per_layer_bytes: int) -> torch.Tensor:
         need = max(self._staging_bytes, 2 * per_layer_bytes + 512)
         if self._staging is None or self._staging.numel() < need:
+            if self._staging is not None:
+                # earlier calls may still be packing into / copying out of the old buffer on the side
+                # streams; it goes back to the allocator only once they are done (growth is rare)
+                self.stream.synchronize()
+                self.dma_stream.synchronize()
             self._staging = torch.empty(need, dtype=torch.uint8, device=self.virtual_page_pool.main_device)
         return self._staging
 
     def _upload(self, ids: np.ndarray, indptr: np.ndarray) -> tuple[torch.Tensor, torch.Tensor]:
-        host = torch.empty(len(ids) + len(indptr), dtype=torch.int32, pin_memory=True)
+        host, slot = _pinned_ring("swap_ids").take(len(ids) + len(indptr))
         host_np = host.numpy()
         host_np[: len(ids)] = ids
         host_np[len(ids) :] = indptr
         dev = host.to(self.virtual_page_pool.main_device, non_blocking=True)
+        _pinned_ring("swap_ids").done(slot)
         return dev[: len(ids)], dev[len(ids) :]
 
     def _move(self, out: bool, id_lists: Sequence[np.ndarray], handles: Sequence[ChunkHandle]) -> None:
@@ -592,7 +615,7 @@ class KVCacheManager:
         with torch.cuda.stream(self.stream):
             ids_dev, indptr_dev = self._upload(ids, indptr)
             fn = _lib.lib.dsv_swap_out_pages if out else _lib.lib.dsv_swap_in_pages
-            common = (pool.layer_stride_bytes, pool.page_bytes, pool.num_layers, ids_dev.data_ptr(),
+            common = (pool.layer_stride_bytes, pool.page_bytes, pool.num_pages, pool.num_layers, ids_dev.data_ptr(),
                       indptr_dev.data_ptr(), indptr.ctypes.data, rows.ctypes.data, len(id_lists),
                       staging.data_ptr(), staging.numel())
             if out:

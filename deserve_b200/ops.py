@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from .pinned import ring as _pinned_ring
 
 _PLAN_HEADER = 8
 
@@ -180,7 +181,7 @@ class BatchDecodeWithPagedKVCacheWrapper:
         cap = plan_capacity(batch, self._sm_count)
         if cap * 4 > self._PLAN_BYTES:
             raise _lib.DeserveKVError(f"decode plan for {batch} requests does not fit the workspace head")
-        pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        pinned, slot = _pinned_ring("decode_plan").take(cap)
         plan = pinned.numpy()
         used, ws_bytes = make_decode_plan(indptr_host, num_qo_heads, num_kv_heads, head_dim, page_size,
                                           data_type if isinstance(data_type, torch.dtype) else torch.float16,
@@ -188,6 +189,7 @@ class BatchDecodeWithPagedKVCacheWrapper:
         if ws_bytes > self._ws.numel() - self._PLAN_BYTES:
             raise _lib.DeserveKVError(f"workspace_buffer too small: split-KV partials need {ws_bytes} bytes")
         self._ws[: used * 4].view(torch.int32).copy_(pinned[:used], non_blocking=True)
+        _pinned_ring("decode_plan").done(slot)
         self._plan_pinned, self._plan_host = pinned, plan
         self._desc = (indptr, indices, last_page_len, num_qo_heads, num_kv_heads, head_dim, page_size)
 
@@ -317,7 +319,7 @@ class BatchPrefillWithPagedKVCacheWrapper:
                 split, total = False, cap
             if cap * 4 > self._PLAN_BYTES:
                 raise _lib.DeserveKVError(f"prefill plan for {nnz} tokens does not fit the workspace head")
-        pinned = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        pinned, slot = _pinned_ring("prefill_plan").take(total)
         buf = pinned.numpy()
         used = make_prefill_plan(qo_indptr_host, kv_len, num_qo_heads, num_kv_heads, head_dim, page_size, dtype, causal,
                                  buf[:cap], min_new_tokens=2 if split else 0)
@@ -345,6 +347,7 @@ class BatchPrefillWithPagedKVCacheWrapper:
                 pos += n
             self._dec = (o_plan, d_used, o_ip, o_last, o_rows, o_idx, len(dec), int(sub_indptr[-1]), buf[o_plan : o_plan + d_used])
         self._ws[: end * 4].view(torch.int32).copy_(pinned[:end], non_blocking=True)
+        _pinned_ring("prefill_plan").done(slot)
         self._pinned, self._plan_host = pinned, buf
         self._desc = (qo_indptr, paged_kv_indptr, paged_kv_indices, paged_kv_last_page_len, num_qo_heads, head_dim, causal)
 

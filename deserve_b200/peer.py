@@ -24,15 +24,21 @@ import torch
 from . import _lib
 
 _FLAG_INTS = 16          # data[2], credit[2], padding: one 64-byte line
-MAX_POLLS = 1 << 24      # about three seconds of polling before a wait gives up
+WAIT_TIMEOUT_NS = 20 * 10**9  # a wait gives up after this much GPU time (ranks may be seconds apart on the host)
+
+
+class PeerHopTimeout(_lib.DeserveKVError):
+    """A bounded wait on a neighbour's flag ran out: a message or a credit never arrived."""
 
 
 class PeerHop:
     """One rank's end of the ring: receives from (rank - 1), sends to (rank + 1)."""
 
-    def __init__(self, rank: int, world: int, message_shape, dtype: torch.dtype, device: torch.device, group):
+    def __init__(self, rank: int, world: int, message_shape, dtype: torch.dtype, device: torch.device, group,
+                 timeout_ns: int = WAIT_TIMEOUT_NS):
         import torch.distributed._symmetric_memory as symm_mem
 
+        self.timeout_ns = int(timeout_ns)
         _lib.require_cuda(torch.empty(0, device=device))
         self.rank, self.world = rank, world
         self.shape, self.dtype = tuple(message_shape), dtype
@@ -70,7 +76,7 @@ class PeerHop:
             raise ValueError("peer hop: message differs from the shape / dtype the ring was set up for")
         k, st = self.sent, _lib.current_stream_ptr(y.device)
         if k >= 2:  # the buffer still holds message k - 2 until the receiver says otherwise
-            _lib.check(_lib.lib.dsv_peer_wait(self._flag(self._mem, 1, k), k - 1, MAX_POLLS, st))
+            _lib.check(_lib.lib.dsv_peer_wait(self._flag(self._mem, 1, k), k - 1, self.timeout_ns, st))
             self.launches += 1
         _lib.check(_lib.lib.dsv_peer_push(self._buf(self._next_mem, k), y.data_ptr(), self.msg_bytes,
                                           self._flag(self._next_mem, 0, k), k + 1, self._arrivals.data_ptr(),
@@ -83,7 +89,7 @@ class PeerHop:
         valid for kernels launched after this call on the current stream, until
         release() of this message."""
         k, st = self.received, _lib.current_stream_ptr(self._mem.device)
-        _lib.check(_lib.lib.dsv_peer_wait(self._flag(self._mem, 0, k), k + 1, MAX_POLLS, st))
+        _lib.check(_lib.lib.dsv_peer_wait(self._flag(self._mem, 0, k), k + 1, self.timeout_ns, st))
         self.launches += 1
         off = (k % 2) * self.msg_bytes
         return self._mem[off : off + self.msg_bytes].view(self.dtype).view(self.shape)
@@ -96,6 +102,20 @@ class PeerHop:
         self.received += 1
         self.launches += 1
 
+    def check(self) -> None:
+        """Synchronise the device and raise PeerHopTimeout if a wait of this process gave up
+        (the status word is cleared by the read). After a timeout the device side of the hop
+        has stopped pushing and crediting, so the data received since is not to be used."""
+        status = _lib.read_device_status()
+        if status == 4:
+            raise PeerHopTimeout(f"rank {self.rank}: a peer-memory wait timed out after {self.timeout_ns / 1e9:.1f} s "
+                                 f"(sent {self.sent}, received {self.received} messages)")
+        if status != 0:
+            raise _lib.DeserveKVError(f"device self-check fired: status {status}")
+
     def close(self) -> None:
-        torch.cuda.synchronize(self._mem.device)
-        self._handle.barrier()
+        """Drain, verify that no wait gave up, and leave together with the neighbours."""
+        try:
+            self.check()
+        finally:
+            self._handle.barrier()

@@ -1,0 +1,59 @@
+"""Reusable pinned host buffers for the small per-step uploads (descriptors,
+attention plans, page-id lists).
+
+The step path uploads a few KB to a few hundred KB of int32 metadata per
+microbatch step. Asking the pinned allocator for a fresh buffer each time costs
+host time on the critical path; a ring of a few buffers that are reused once the
+copy that read them has finished does not. The reference builds the same arrays
+with torch.tensor(..., device="cuda") from pageable memory, one blocking copy
+each (deserve_worker/model/context/flash.py:50-64).
+"""
+from __future__ import annotations
+
+import torch
+
+
+class PinnedRing:
+    """`slots` pinned int32 buffers handed out round-robin.
+
+    take(n) returns (buffer[:n], slot). After queuing the host->device copy that
+    reads the buffer, call done(slot) on the stream of the copy; the slot is then
+    reused only after that copy has finished. Host-side readers of a buffer (a C
+    call that reads a plan header during the step) stay valid for slots - 1
+    further take() calls."""
+
+    def __init__(self, slots: int = 8, capacity: int = 1 << 14, pin: bool | None = None):
+        self._pin = torch.cuda.is_available() if pin is None else pin
+        self._bufs = [torch.empty(capacity, dtype=torch.int32, pin_memory=self._pin) for _ in range(slots)]
+        self._events: list = [None] * slots
+        self._next = 0
+
+    def take(self, n: int) -> tuple[torch.Tensor, int]:
+        slot = self._next
+        self._next = (slot + 1) % len(self._bufs)
+        ev = self._events[slot]
+        if ev is not None:
+            ev.synchronize()  # the copy queued slots steps ago: long done in steady state
+            self._events[slot] = None
+        if self._bufs[slot].numel() < n:
+            self._bufs[slot] = torch.empty(max(n, 2 * self._bufs[slot].numel()), dtype=torch.int32, pin_memory=self._pin)
+        return self._bufs[slot][:n], slot
+
+    def done(self, slot: int, stream=None) -> None:
+        if not self._pin:
+            return
+        ev = self._events[slot]
+        if ev is None:
+            ev = self._events[slot] = torch.cuda.Event()
+        ev.record(stream if stream is not None else torch.cuda.current_stream())
+
+
+_RINGS: dict = {}
+
+
+def ring(name: str, slots: int = 8, capacity: int = 1 << 14) -> PinnedRing:
+    """Process-wide ring by name (one per kind of upload)."""
+    r = _RINGS.get(name)
+    if r is None:
+        r = _RINGS[name] = PinnedRing(slots, capacity)
+    return r

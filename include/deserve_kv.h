@@ -247,15 +247,19 @@ int dsv_paged_decode_static(const void* q, int64_t q_stride_tok, const void* pag
  * (page_bytes each). That is the chunk layout of
  * KVCacheManager.copy_gpu_to_cpu / copy_cpu_to_gpu
  * (deserve_worker/kvcache/manager.py:38-44, 63-73). page_ids and ids_indptr
- * (n_tasks+1 entries) are DEVICE arrays. Bit-exact.
+ * (n_tasks+1 entries) are DEVICE arrays. num_pages: pages in a layer slab
+ * (layer_stride_bytes >= num_pages * page_bytes is checked on the host); a page
+ * id outside [0, num_pages) is skipped — nothing is read or written for that
+ * row — and recorded in the device status word. Bit-exact.
  */
 int dsv_pack_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
-                   const int32_t* page_ids, const int32_t* ids_indptr, int n_tasks,
-                   int64_t total_ids, int layer_begin, int layer_end, void* dst, void* stream);
+                   int64_t num_pages, const int32_t* page_ids, const int32_t* ids_indptr,
+                   int n_tasks, int64_t total_ids, int layer_begin, int layer_end, void* dst,
+                   void* stream);
 int dsv_unpack_pages(const void* src, void* pages_base, int64_t layer_stride_bytes,
-                     int64_t page_bytes, const int32_t* page_ids, const int32_t* ids_indptr,
-                     int n_tasks, int64_t total_ids, int layer_begin, int layer_end,
-                     void* stream);
+                     int64_t page_bytes, int64_t num_pages, const int32_t* page_ids,
+                     const int32_t* ids_indptr, int n_tasks, int64_t total_ids, int layer_begin,
+                     int layer_end, void* stream);
 
 /*
  * Per-task offload (swap-out) and reload (swap-in) between scattered HBM pages
@@ -270,21 +274,26 @@ int dsv_unpack_pages(const void* src, void* pages_base, int64_t layer_stride_byt
  * host_pool + chunk_row_begin_host[t] * page_bytes and holds
  * num_layers * n_t rows, layer-major. ids_indptr_host is the HOST copy of
  * ids_indptr. Half of the staging buffer must hold one layer of all tasks
- * (total_ids * page_bytes) or the call fails with DSV_E_WORKSPACE.
+ * (total_ids * page_bytes) or the call fails with DSV_E_WORKSPACE. num_pages
+ * bounds the page ids as in dsv_pack_pages.
  * Asynchronous: the caller waits on both streams (swap-out: host data valid
- * after stream_dma; swap-in: pages valid after stream_kernel).
+ * after stream_dma; swap-in: pages valid after stream_kernel). Calls that share
+ * `staging` may follow one another without a host wait as long as they also
+ * share the two streams and the four events: every window first waits for the
+ * event that marks the last use of its staging half, whichever call recorded it.
  */
 int dsv_swap_out_pages(const void* pages_base, int64_t layer_stride_bytes, int64_t page_bytes,
-                       int num_layers, const int32_t* page_ids, const int32_t* ids_indptr,
-                       const int32_t* ids_indptr_host, const int64_t* chunk_row_begin_host,
-                       int n_tasks, void* staging, int64_t staging_bytes, void* host_pool,
-                       void* stream_kernel, void* stream_dma, void** events);
+                       int64_t num_pages, int num_layers, const int32_t* page_ids,
+                       const int32_t* ids_indptr, const int32_t* ids_indptr_host,
+                       const int64_t* chunk_row_begin_host, int n_tasks, void* staging,
+                       int64_t staging_bytes, void* host_pool, void* stream_kernel,
+                       void* stream_dma, void** events);
 int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_stride_bytes,
-                      int64_t page_bytes, int num_layers, const int32_t* page_ids,
-                      const int32_t* ids_indptr, const int32_t* ids_indptr_host,
-                      const int64_t* chunk_row_begin_host, int n_tasks, void* staging,
-                      int64_t staging_bytes, void* stream_kernel, void* stream_dma,
-                      void** events);
+                      int64_t page_bytes, int64_t num_pages, int num_layers,
+                      const int32_t* page_ids, const int32_t* ids_indptr,
+                      const int32_t* ids_indptr_host, const int64_t* chunk_row_begin_host,
+                      int n_tasks, void* staging, int64_t staging_bytes, void* stream_kernel,
+                      void* stream_dma, void** events);
 
 /*
  * Microbatch region swap: for every layer l, copy the slab
@@ -344,15 +353,19 @@ int dsv_host_build_step(uint8_t* bitmap, int32_t num_pages, int32_t* buffer, int
  *   dsv_peer_signal writes `value` to *flag after a system-wide fence (credits going back
  *                   to the sender).
  *   dsv_peer_wait   holds the stream until *flag >= value: one thread polls with
- *                   acquire loads, at most max_polls times; on expiry the kernel ends,
- *                   the device status reads 4 (wait timeout) and the stream continues.
+ *                   acquire loads for at most timeout_ns nanoseconds of the GPU's global
+ *                   timer; on expiry the kernel ends, the device status reads 4 (wait
+ *                   timeout) and the stream continues.
  * Flags are int32 that only grow (message number + 1). No TMA, no multicast: peer
- * memory is written with ordinary stores only.
+ * memory is written with ordinary stores only. While the status word holds a wait
+ * timeout, later pushes, signals and waits of the process do nothing (a link that lost a
+ * message must not credit or overwrite buffers); dsv_read_device_status reports and
+ * clears it.
  */
 int dsv_peer_push(void* dst, const void* src, int64_t bytes, int32_t* flag, int32_t value,
                   uint32_t* arrivals, int sm_count, void* stream);
 int dsv_peer_signal(int32_t* flag, int32_t value, void* stream);
-int dsv_peer_wait(const int32_t* flag, int32_t value, int64_t max_polls, void* stream);
+int dsv_peer_wait(const int32_t* flag, int32_t value, int64_t timeout_ns, void* stream);
 
 /*
  * Self-test of the bounded waits every mbarrier-based kernel here uses: launches

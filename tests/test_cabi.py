@@ -40,8 +40,13 @@ def test_invalid_arguments_return_codes_not_crashes():
     buf = (ctypes.c_char * 64)()
     assert L.dsv_region_swap(buf, 4, 1024, 512, 1024, buf, None, None, None, None) == -1
     assert "outside a layer" in _lib.last_error()
-    assert L.dsv_pack_pages(buf, 1024, 100, buf, buf, 1, 1, 0, 1, buf, None) == -1
+    assert L.dsv_pack_pages(buf, 1024, 100, 4, buf, buf, 1, 1, 0, 1, buf, None) == -1
     assert "multiple of 16" in _lib.last_error()
+    # a layer slab that cannot hold num_pages pages is refused before anything is launched
+    assert L.dsv_pack_pages(buf, 1024, 256, 5, buf, buf, 1, 1, 0, 1, buf, None) == -1
+    assert "cannot hold" in _lib.last_error()
+    assert L.dsv_unpack_pages(buf, buf, 1024, 256, 0, buf, buf, 1, 1, 0, 1, None) == -1
+    assert "num_pages" in _lib.last_error()
     with pytest.raises(ValueError):
         _lib.check(-1)
     with pytest.raises(_lib.DeserveKVError):

@@ -27,23 +27,34 @@ def test_push_signal_wait_on_one_gpu():
         src += 1
         _lib.check(_lib.lib.dsv_peer_push(dst.data_ptr(), src.data_ptr(), src.numel() * 4, flags.data_ptr(), k + 1,
                                           arrivals.data_ptr(), 0, st))
-        _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr(), k + 1, 1 << 20, st))
+        _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr(), k + 1, 10**9, st))
         torch.cuda.synchronize()
         assert torch.equal(dst, src) and int(flags[0]) == k + 1 and int(arrivals[0]) == 0
     _lib.check(_lib.lib.dsv_peer_signal(flags.data_ptr() + 4, 7, st))
     torch.cuda.synchronize()
     assert int(flags[1]) == 7
     assert _lib.read_device_status() == 0
-    # a flag nobody raises: the wait gives up, the status word says so, the context lives on
-    _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr() + 8, 1, 2000, st))
+    # a flag nobody raises: the wait gives up after 2 ms of GPU time, the status word says so, the
+    # context lives on. While the status is unread the link counts as broken: a credit and a push
+    # queued behind the failed wait are dropped, a second wait returns at once.
+    _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr() + 8, 1, 2_000_000, st))
+    _lib.check(_lib.lib.dsv_peer_signal(flags.data_ptr() + 12, 9, st))
+    _lib.check(_lib.lib.dsv_peer_push(dst.data_ptr(), (src + 5).data_ptr(), src.numel() * 4, flags.data_ptr(), 99,
+                                      arrivals.data_ptr(), 0, st))
+    _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr() + 8, 1, 500 * 10**9, st))
     torch.cuda.synchronize()
+    assert int(flags[3]) == 0 and int(flags[0]) == 3 and torch.equal(dst, src)
     assert _lib.read_device_status() == 4
     assert _lib.read_device_status() == 0
-    assert torch.equal(dst, src)
+    _lib.check(_lib.lib.dsv_peer_signal(flags.data_ptr() + 12, 9, st))  # status read: the link works again
+    torch.cuda.synchronize()
+    assert int(flags[3]) == 9
     with pytest.raises(ValueError):
         _lib.check(_lib.lib.dsv_peer_push(dst.data_ptr(), src.data_ptr(), 10, flags.data_ptr(), 1, arrivals.data_ptr(), 0, st))
     with pytest.raises(ValueError):
         _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr(), 1, 0, st))
+    with pytest.raises(ValueError):
+        _lib.check(_lib.lib.dsv_peer_wait(flags.data_ptr(), 1, 601 * 10**9, st))
 
 
 def _stage_math(rank, m, s, x):
@@ -75,9 +86,11 @@ def _worker(rank, world, port, steps, q):
         pipe.advance(1)
         if rank == world - 1 and len(pipe.completed) > before:
             finals[pipe.completed[-1]] = pipe.last_output.clone()
-    torch.cuda.synchronize()
-    status = _lib.read_device_status()
-    hop.close()
+    status = 0
+    try:
+        hop.close()  # raises if a wait of this rank gave up
+    except _lib.DeserveKVError:
+        status = 4
     q.put((rank, status, {k: v.cpu().tolist() for k, v in finals.items()}))
     dist.barrier()
     dist.destroy_process_group()

@@ -97,7 +97,7 @@ def test_pack_unpack_roundtrip_bit_exact(dtype):
     for l0, l1 in [(0, L), (1, 3)]:
         w = l1 - l0
         packed = torch.zeros(sum(counts) * w, *pool.pages.shape[2:], dtype=dtype, device=DEV)
-        _lib.check(_lib.lib.dsv_pack_pages(pool.pages.data_ptr(), pool.layer_stride_bytes, pool.page_bytes,
+        _lib.check(_lib.lib.dsv_pack_pages(pool.pages.data_ptr(), pool.layer_stride_bytes, pool.page_bytes, P,
                                            ids.data_ptr(), indptr.data_ptr(), len(counts), sum(counts), l0, l1,
                                            packed.data_ptr(), _lib.current_stream_ptr(DEV)))
         want = torch.cat([swap_ops.offload_rows(ref[l0:l1], x) for x in id_lists])
@@ -108,7 +108,7 @@ def test_pack_unpack_roundtrip_bit_exact(dtype):
         ids2 = torch.tensor(np.concatenate(id_lists2), dtype=torch.int32, device=DEV)
         before = pool.pages.cpu()
         _lib.check(_lib.lib.dsv_unpack_pages(packed.data_ptr(), pool.pages.data_ptr(), pool.layer_stride_bytes,
-                                             pool.page_bytes, ids2.data_ptr(), indptr.data_ptr(), len(counts),
+                                             pool.page_bytes, P, ids2.data_ptr(), indptr.data_ptr(), len(counts),
                                              sum(counts), l0, l1, _lib.current_stream_ptr(DEV)))
         at = 0
         for x, n in zip(id_lists2, counts):
@@ -184,3 +184,75 @@ def test_single_task_reference_api():
     got = pool.pages.cpu()
     assert torch.equal(got[:, torch.as_tensor(new, dtype=torch.long)].view(torch.uint8),
                        ref[:, torch.as_tensor(old, dtype=torch.long)].view(torch.uint8))
+
+
+@pytest.mark.parametrize("staging_mib", [None, 24])
+def test_back_to_back_offloads_then_reloads_share_the_staging_buffer(staging_mib):
+    """The reference offloads and reloads task by task in a loop
+    (deserve_worker/engine/microbatch/processor.py:62-88). Here every such call is
+    asynchronous and all of them go through one staging buffer, so consecutive calls
+    with NO host wait in between must order themselves on the device: a task is
+    large enough (64 MiB) that its DMA is still running when the next call's pack
+    kernel (or host->device burst) wants the same staging half."""
+    L, ps, hkv, d = 8, 16, 8, 128
+    n_tasks, n_pages = 4, 128
+    dtype = torch.bfloat16
+    pool = dk.VirtualPagePool(L, 2 * n_tasks * n_pages + 8, 0, ps, DEV, dtype, n_kv_heads=hkv, head_dim=d)
+    g = torch.Generator(device=DEV).manual_seed(11)
+    pool.pages.normal_(0.0, 1.0, generator=g)
+    pta = dk.PageTableAllocator(2 * n_tasks, n_pages * ps, ps, DEV)
+    chunks = dk.CpuChunkPool(L, 10, ps, dtype, n_kv_heads=hkv, head_dim=d)  # 512 page rows of every layer
+    mgr = dk.KVCacheManager(pool, chunks, pta, staging_bytes=None if staging_mib is None else staging_mib << 20)
+    caches = []
+    for _ in range(n_tasks):
+        c = dk.VirtualPagedKVCache.empty(pta, pool)
+        c.extend(n_pages * ps)
+        caches.append(c)
+    id_lists = [c.page_table.retrieve().numpy().copy() for c in caches]
+    ref = pool.pages.cpu()
+    handles = [mgr.copy_gpu_to_cpu(c, f"t{i}") for i, c in enumerate(caches)]  # no wait in between
+    mgr.synchronize()
+    rows = [swap_ops.offload_rows(ref, ids) for ids in id_lists]
+    for h, want in zip(handles, rows):
+        assert torch.equal(h.retrieve()[: n_pages * L].view(torch.uint8), want.view(torch.uint8))
+    for c in caches:
+        c.free()
+    pool.pages.fill_(-3.0)
+    filler = dk.VirtualPagedKVCache.empty(pta, pool)
+    filler.extend(5 * ps)  # shifts the ids the reloads get
+    ref = pool.pages.cpu()
+    new_caches = [mgr.copy_cpu_to_gpu(h, f"t{i}") for i, h in enumerate(handles)]  # no wait in between
+    mgr.synchronize()
+    for c, want in zip(new_caches, rows):
+        swap_ops.reload_rows(ref, c.page_table.retrieve().numpy(), want)
+    assert torch.equal(pool.pages.cpu().view(torch.uint8), ref.view(torch.uint8))
+
+
+def test_pack_skips_page_ids_outside_the_pool_and_reports_them():
+    """An id >= num_pages (a stale table entry) or < 0 touches no memory: the row
+    is skipped, the other rows are copied, and the status word reads 1 (bad page
+    id). The check replaces the access; nothing faults."""
+    L, P, ps, hkv, d = 2, 12, 16, 2, 64
+    pool = dk.GpuPagePool(L, P, ps, DEV, torch.bfloat16, n_kv_heads=hkv, head_dim=d)
+    ref = _fill(pool, 9)
+    ids_host = np.array([3, P + 5, 7, -2, 0], dtype=np.int32)
+    ids = torch.from_numpy(ids_host).to(DEV)
+    indptr = torch.tensor([0, len(ids_host)], dtype=torch.int32, device=DEV)
+    packed = torch.zeros(len(ids_host) * L, *pool.pages.shape[2:], dtype=torch.bfloat16, device=DEV)
+    _lib.check(_lib.lib.dsv_pack_pages(pool.pages.data_ptr(), pool.layer_stride_bytes, pool.page_bytes, P,
+                                       ids.data_ptr(), indptr.data_ptr(), 1, len(ids_host), 0, L, packed.data_ptr(),
+                                       _lib.current_stream_ptr(DEV)))
+    assert _lib.read_device_status() == 1
+    got = packed.cpu().view(L, len(ids_host), *pool.pages.shape[2:])
+    for j, pid in enumerate(ids_host.tolist()):
+        if 0 <= pid < P:
+            assert torch.equal(got[:, j], ref[:, pid])
+        else:
+            assert not got[:, j].any()
+    # the scatter direction: rows with a bad id leave the pool untouched
+    before = pool.pages.cpu()
+    _lib.check(_lib.lib.dsv_unpack_pages(packed.data_ptr(), pool.pages.data_ptr(), pool.layer_stride_bytes,
+                                         pool.page_bytes, P, ids.data_ptr(), indptr.data_ptr(), 1, len(ids_host), 0, L,
+                                         _lib.current_stream_ptr(DEV)))
+    assert _lib.read_device_status() == 1
+    assert torch.equal(pool.pages.cpu().view(torch.uint8), before.view(torch.uint8))

@@ -252,3 +252,34 @@ def test_allocator_agrees_with_oracle_on_random_histories(seed, native):
         assert pool.num_avails == opool.num_avails
         assert pool.page_buffer.tolist() == opool.buffer.tolist()
         assert pool.page_bitmap.numpy().tolist() == opool.bitmap.tolist()
+
+
+def test_reserve_takes_chosen_pages_out_of_the_free_set():
+    pool = dk.CpuPagePool(1, 32, 4, torch.float32, n_kv_heads=1, head_dim=4)
+    ids = np.array([30, 2, 17], dtype=np.int32)
+    pool.reserve(ids)
+    assert pool.num_avails == 29 and not pool.page_bitmap[ids.astype(np.int64)].any()
+    got = pool.alloc(4).tolist()
+    assert got == [0, 1, 3, 4]  # lowest free ids, the reserved ones skipped
+    with pytest.raises(ValueError):
+        pool.reserve([2])        # already taken
+    with pytest.raises(ValueError):
+        pool.reserve([5, 5])     # listed twice
+    with pytest.raises(ValueError):
+        pool.reserve([32])       # outside the pool
+    pool.free(ids)
+    assert pool.num_avails == 28
+
+
+def test_pinned_ring_hands_out_buffers_round_robin_and_grows():
+    from deserve_b200.pinned import PinnedRing
+
+    r = PinnedRing(slots=3, capacity=8, pin=False)
+    a, sa = r.take(4)
+    b, sb = r.take(8)
+    c, sc = r.take(20)  # larger than the slot: the slot grows
+    assert (sa, sb, sc) == (0, 1, 2) and a.numel() == 4 and c.numel() == 20
+    a[:] = 7
+    r.done(sa)
+    a2, sa2 = r.take(2)
+    assert sa2 == 0 and a2.data_ptr() == a.data_ptr()
