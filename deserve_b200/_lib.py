@@ -65,6 +65,7 @@ _SIGNATURES = {
                                          c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                          c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
     "dsv_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
+    "dsv_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "dsv_greedy_sample": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p]),
     "dsv_decode_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, _p64,
                                 _p64]),
@@ -87,14 +88,18 @@ _SIGNATURES = {
                                    c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "dsv_swap_in_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
-    "dsv_region_swap": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p]),
+    "dsv_region_swap": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p]),
 }
 
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.restype = _res
     _fn.argtypes = _args
+
+
+# kernels of this library launched through the Python operators since the counter was last reset
+LAUNCHES = [0]
 
 
 def last_error() -> str:

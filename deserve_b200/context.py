@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .pinned import ring as _pinned_ring
+from .pinned import COUNTERS as _COUNTERS, ring as _pinned_ring
 from .kvcache import PagedKVCache, PagePool
 from .task import TaskData
 
@@ -104,6 +104,7 @@ class FlashForwardCtx(PagedForwardCtx):
         if on_gpu:
             dev = pinned[:used].to(pool.main_device, non_blocking=True)
             _pinned_ring("descriptors").done(slot)
+            _COUNTERS["h2d_bytes"] += used * 4
         else:
             dev = pinned
         starts = {n: host[n].ctypes.data - pinned.data_ptr() for n in _NAMES}

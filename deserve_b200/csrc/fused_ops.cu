@@ -1,6 +1,8 @@
 // The small kernels either side of the KV path: RMSNorm, rotary embedding fused
 // into the append-scatter, and greedy (argmax) sampling. All are HBM-bound
 // streaming kernels: 16-byte vectors, one pass over the data.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace dsv {
@@ -60,6 +62,32 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
 #pragma unroll
     for (int i = 0; i < N; ++i) f[i] = f[i] * scale * g[i];
     orow[v] = Vec16<T>::pack(f);
+  }
+}
+
+// out[r, c] = silu(gu[r, c]) * gu[r, ffn + c]: the elementwise middle of the SwiGLU feed-forward on
+// the output of one fused gate|up projection. Both factors are rounded to T the way the two torch
+// statements round them (silu, then the product). One thread per 16-byte vector of out.
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t gu_stride, int64_t out_stride, int rows,
+                int ffn) {
+  constexpr int N = Vec16<T>::N;
+  const int vec_per_row = ffn / N;
+  const int64_t total = (int64_t)rows * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row), v = (int)(i % vec_per_row);
+    const uint4* g = reinterpret_cast<const uint4*>(gu + (int64_t)r * gu_stride) + v;
+    const uint4* u = reinterpret_cast<const uint4*>(gu + (int64_t)r * gu_stride + ffn) + v;
+    float a[N], b[N];
+    Vec16<T>::unpack(ld_stream16(g), a);
+    Vec16<T>::unpack(ld_stream16(u), b);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const float s = to_f32(from_f32<T>(a[j] / (1.f + expf(-a[j]))));
+      a[j] = s * b[j];
+    }
+    reinterpret_cast<uint4*>(out + (int64_t)r * out_stride)[v] = Vec16<T>::pack(a);
   }
 }
 
@@ -252,6 +280,35 @@ int dsv_rope_append_paged_kv(void* q, const void* k, const void* v, int64_t q_st
     default: DSV_LAUNCH_RA(__nv_bfloat16);
   }
 #undef DSV_LAUNCH_RA
+  DSV_CUDA(cudaGetLastError());
+  return DSV_OK;
+}
+
+int dsv_silu_mul(const void* gate_up, void* out, int64_t gate_up_stride, int64_t out_stride, int rows, int ffn_dim,
+                 int dtype, void* stream) {
+  using namespace dsv;
+  DSV_REQUIRE(dtype_ok(dtype), "silu_mul: unknown dtype %d", dtype);
+  DSV_REQUIRE(rows >= 0 && ffn_dim > 0, "silu_mul: bad shape");
+  if (rows == 0) return DSV_OK;
+  DSV_REQUIRE(gate_up && out, "silu_mul: null pointer argument");
+  const int es = elem_size(dtype), n = 16 / es;
+  DSV_REQUIRE(ffn_dim % n == 0, "silu_mul: ffn_dim %d must be a multiple of %d", ffn_dim, n);
+  DSV_REQUIRE(aligned16(gate_up) && aligned16(out) && (gate_up_stride * es) % 16 == 0 && (out_stride * es) % 16 == 0,
+              "silu_mul: pointers and strides must be 16-byte aligned");
+  DSV_REQUIRE(gate_up_stride >= 2 * (int64_t)ffn_dim && out_stride >= ffn_dim, "silu_mul: row stride smaller than a row");
+  const int64_t total = (int64_t)rows * (ffn_dim / n);
+  const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case DSV_F32:
+      silu_mul_kernel<float><<<grid, 256, 0, st>>>((const float*)gate_up, (float*)out, gate_up_stride, out_stride, rows, ffn_dim);
+      break;
+    case DSV_F16:
+      silu_mul_kernel<__half><<<grid, 256, 0, st>>>((const __half*)gate_up, (__half*)out, gate_up_stride, out_stride, rows, ffn_dim);
+      break;
+    default:
+      silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, gate_up_stride, out_stride, rows, ffn_dim);
+  }
   DSV_CUDA(cudaGetLastError());
   return DSV_OK;
 }

@@ -245,16 +245,21 @@ int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_str
 }
 
 int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes,
-                    int64_t region_offset_bytes, int64_t region_bytes, void* host_out,
-                    const void* host_in, void* stream_out, void* stream_in, void* event) {
+                    int64_t region_offset_bytes, int64_t region_bytes, int64_t out_bytes, int64_t in_bytes,
+                    void* host_out, const void* host_in, void* stream_out, void* stream_in, void* event) {
   using namespace dsv;
   DSV_REQUIRE(num_layers >= 0 && region_bytes >= 0, "region_swap: negative size");
-  if (num_layers == 0 || region_bytes == 0 || (host_out == nullptr && host_in == nullptr)) return DSV_OK;
+  DSV_REQUIRE(out_bytes >= 0 && out_bytes <= region_bytes && in_bytes >= 0 && in_bytes <= region_bytes,
+              "region_swap: out_bytes (%lld) and in_bytes (%lld) must lie in [0, region_bytes = %lld]",
+              (long long)out_bytes, (long long)in_bytes, (long long)region_bytes);
+  if (host_out == nullptr) out_bytes = 0;
+  if (host_in == nullptr) in_bytes = 0;
+  if (num_layers == 0 || (out_bytes == 0 && in_bytes == 0)) return DSV_OK;
   DSV_REQUIRE(pages_base != nullptr, "region_swap: null pages_base");
   DSV_REQUIRE(region_offset_bytes >= 0 && region_offset_bytes + region_bytes <= layer_stride_bytes,
               "region_swap: region [%lld,+%lld) outside a layer of %lld bytes", (long long)region_offset_bytes,
               (long long)region_bytes, (long long)layer_stride_bytes);
-  const bool both = host_out != nullptr && host_in != nullptr;
+  const bool both = out_bytes > 0 && in_bytes > 0;
   DSV_REQUIRE(!both || event != nullptr, "region_swap: an event is needed when both directions are given");
   unsigned char* dev = static_cast<unsigned char*>(pages_base) + region_offset_bytes;
   cudaStream_t s_out = (cudaStream_t)stream_out, s_in = (cudaStream_t)stream_in;
@@ -262,21 +267,21 @@ int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes
   const int group = std::max(1, (num_layers + 7) / 8);
   for (int l0 = 0; l0 < num_layers; l0 += group) {
     const int l1 = std::min(num_layers, l0 + group);
-    if (host_out != nullptr) {
+    if (out_bytes > 0) {
       for (int l = l0; l < l1; ++l)
         DSV_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(host_out) + (int64_t)l * region_bytes,
-                                 dev + (int64_t)l * layer_stride_bytes, (size_t)region_bytes, cudaMemcpyDeviceToHost,
+                                 dev + (int64_t)l * layer_stride_bytes, (size_t)out_bytes, cudaMemcpyDeviceToHost,
                                  s_out));
       if (both) {
         DSV_CUDA(cudaEventRecord((cudaEvent_t)event, s_out));
         DSV_CUDA(cudaStreamWaitEvent(s_in, (cudaEvent_t)event, 0));
       }
     }
-    if (host_in != nullptr) {
+    if (in_bytes > 0) {
       for (int l = l0; l < l1; ++l)
         DSV_CUDA(cudaMemcpyAsync(dev + (int64_t)l * layer_stride_bytes,
                                  static_cast<const unsigned char*>(host_in) + (int64_t)l * region_bytes,
-                                 (size_t)region_bytes, cudaMemcpyHostToDevice, s_in));
+                                 (size_t)in_bytes, cudaMemcpyHostToDevice, s_in));
     }
   }
   return DSV_OK;

@@ -26,6 +26,7 @@ from .context import FlashDecodeCtx
 from .kvcache import PagedKVCache
 from .task import TaskData
 from .request import StepRequest  # noqa: F401  (re-exported: the stage loop's input type)
+from .trace import phase
 
 
 @dataclass
@@ -71,13 +72,17 @@ class KVStage:
         self.workspace = torch.empty(workspace_bytes, dtype=torch.uint8, device=pool.main_device)
 
     def forward(self, x: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, sd: StepDescriptors,
-                on_attention: Callable[[int], None] | None = None) -> torch.Tensor:
+                on_attention: Callable[[int], None] | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         """x: [B, Hq, D] query of the first layer; layer l's attention output is
         layer l+1's query. k_new, v_new: [layers, B, Hkv, D] rows to append.
         on_attention(i), if given, is called before and after every attention
-        launch (i = 2*layer, 2*layer+1) so a caller can bracket it with events."""
+        launch (i = 2*layer, 2*layer+1) so a caller can bracket it with events.
+        out, if given, receives the last layer's output: the attention kernel then
+        stores its result straight into that buffer, which may be the next stage's
+        inbox in peer memory (the compute kernel itself does the hop)."""
         if sd.workspace_bytes > self.workspace.numel():
             raise RuntimeError(f"stage workspace too small: need {sd.workspace_bytes} bytes")
+        n = self.layer_end - self.layer_begin
         for i, layer in enumerate(range(self.layer_begin, self.layer_end)):
             pages = self.pool.pages[layer]
             ops.append_paged_kv_cache(k_new[i], v_new[i], sd.indptr, pages, sd.kv_page_indices, sd.kv_page_indptr,
@@ -85,87 +90,164 @@ class KVStage:
             if on_attention is not None:
                 on_attention(2 * i)
             x = ops.paged_decode(x, pages, sd.kv_page_indices, sd.kv_page_indptr, sd.kv_last_page_lens, sd.plan_host,
-                                 sd.plan_dev, self.workspace)
+                                 sd.plan_dev, self.workspace, out=out if i == n - 1 else None)
             if on_attention is not None:
                 on_attention(2 * i + 1)
         return x
 
 
-class RingPipeline:
-    """W stages (ranks) and W microbatches in a ring. In slot t, rank r works on
-    unit u = t - r, i.e. microbatch u % W at token step u // W, then every rank
-    hands its output to rank (r+1) % W in one grouped send+recv. After the first
-    W-1 slots every rank is busy in every slot. The object keeps its position,
-    so a caller can run some slots, synchronise, and continue with a full ring.
+def make_ring_links(dist, rank: int, world: int):
+    """One two-rank process group per directed link r -> (r+1) % world, created in
+    the same order on every rank. Returns (group this rank sends on, group it
+    receives on). A link carries traffic in one direction only, so a receive
+    posted early never sits in front of a send on the same communicator (one
+    communicator for the whole ring would need grouped send+recv calls, which tie
+    a stage's send to its neighbour's progress)."""
+    if world < 2:
+        return None, None
+    groups = [dist.new_group([r, (r + 1) % world]) for r in range(world)]
+    return groups[rank], groups[(rank - 1) % world]
 
-    stage_fn(unit, microbatch, token_step, x) -> y runs the rank's layers.
+
+class RingPipeline:
+    """W stages (ranks) and M >= W microbatches in a ring. In slot t, rank r works on
+    unit u = t - r, i.e. microbatch u % M at token step u // M, and hands its output
+    to rank (r+1) % W; the last stage feeds the first. After the first W-1 slots
+    every rank is busy in every slot. The object keeps its position, so a caller
+    can run some slots, synchronise, and continue with a full ring.
+
+    The hop never blocks the host, and blocks the compute stream only where the data
+    is needed: the receive for slot t+1 is posted before slot t computes, the send
+    of slot t's output is queued behind it, and the compute stream waits for a
+    message right before the kernels that read it. Three transports:
+      * links=(send_group, recv_group) from make_ring_links: NCCL (or gloo)
+        isend / irecv, one communicator per directed link;
+      * peer_hop (deserve_b200.peer.PeerHop): the sender stores into the next GPU's
+        inbox; with direct=True the stage's last kernel writes its output there
+        itself (stage_fn gets out=<inbox buffer>) and only a flag follows;
+      * neither (W == 1): the output is the next input.
+
+    stage_fn(unit, microbatch, token_step, x[, out=...]) -> y runs the rank's layers.
     first_input(microbatch) gives rank 0 its input for token step 0.
+    recv_spec(unit) -> (shape, dtype, device) of the tensor this rank consumes as
+    input of `unit`; None: same as what first_input / the previous message had.
     """
 
     def __init__(self, rank: int, world: int, stage_fn, first_input, total_steps: int, group=None, dist=None,
-                 recv_spec=None, peer_hop=None):
-        # recv_spec(unit) -> (shape, dtype, device) of the tensor this rank consumes as input of `unit`;
-        # None: same shape as what it sends
+                 recv_spec=None, peer_hop=None, microbatches: int | None = None, links=None, direct: bool = False):
         self.recv_spec = recv_spec
-        # peer_hop (deserve_b200.peer.PeerHop): messages go through peer memory instead of NCCL send/recv
         self.peer_hop = peer_hop
+        self.direct = direct and peer_hop is not None
         self.rank, self.world = rank, world
+        self.M = world if microbatches is None else microbatches
+        if self.M < world:
+            raise ValueError(f"{self.M} microbatches cannot keep {world} stages busy")
+        if peer_hop is not None and getattr(peer_hop, "depth", 2) < self.M - world + 2:
+            raise ValueError("peer hop: the inbox needs microbatches - stages + 2 buffers")
         self.stage_fn, self.first_input = stage_fn, first_input
-        self.units = total_steps * world
-        self.group = group
+        self.units = total_steps * self.M
         self.dist = dist
+        if world > 1 and peer_hop is None and links is None:
+            links = make_ring_links(dist, rank, world)
+        self.send_group, self.recv_group = links if links is not None else (None, None)
         self.slot = 0
-        self.inbox: torch.Tensor | None = None
         self.last_output: torch.Tensor | None = None
         self.completed: list[tuple[int, int]] = []  # (microbatch, token_step) finished on the last rank
+        self._carry: dict = {}                       # W == 1: microbatch -> the output that is its next input
+        self._posted: dict = {}                      # slot -> (work, buffer) of receives in flight
+        self._sends: list = []                       # (work, tensor) of sends in flight (keeps the tensor alive)
+        self._like = None
+
+    # ---- schedule ---------------------------------------------------------------------------
+    def _unit(self, rank: int, slot: int) -> int | None:
+        u = slot - rank
+        return u if 0 <= u < self.units else None
 
     def _computes(self, rank: int, slot: int) -> bool:
-        return 0 <= slot - rank < self.units
+        return self._unit(rank, slot) is not None
 
+    def _from_hop(self, slot: int) -> bool:
+        """Does this rank's input of `slot` arrive over the hop?"""
+        u = self._unit(self.rank, slot)
+        return u is not None and self.world > 1 and not (self.rank == 0 and u < self.M)
+
+    def _sends_after(self, slot: int) -> bool:
+        """Is this rank's output of `slot` somebody's input? (The last stage's output of a
+        microbatch's final token step is not.)"""
+        u = self._unit(self.rank, slot)
+        return u is not None and self.world > 1 and (self.rank < self.world - 1 or u + self.M < self.units)
+
+    # ---- NCCL / gloo links ---------------------------------------------------------------------
+    def _post_recv(self, slot: int) -> None:
+        if slot in self._posted or not self._from_hop(slot):
+            return
+        if self.recv_spec is not None:
+            shape, dtype, device = self.recv_spec(self._unit(self.rank, slot))
+            buf = torch.empty(shape, dtype=dtype, device=device)
+        else:
+            buf = torch.empty_like(self._like if self._like is not None else self.first_input(0))
+        prv = (self.rank - 1) % self.world
+        self._posted[slot] = (self.dist.irecv(buf, prv, group=self.recv_group), buf)
+
+    def _take_recv(self, slot: int) -> torch.Tensor:
+        self._post_recv(slot)
+        work, buf = self._posted.pop(slot)
+        with phase("recv"):
+            work.wait()  # NCCL: the compute stream waits for the message; gloo: the host does
+        return buf
+
+    def _send(self, y: torch.Tensor) -> None:
+        nxt = (self.rank + 1) % self.world
+        self._sends = [(w, t) for w, t in self._sends if not w.is_completed()]
+        with phase("send"):
+            self._sends.append((self.dist.isend(y, nxt, group=self.send_group), y))
+
+    def flush(self) -> None:
+        """Wait for the sends still in flight (end of a run)."""
+        for w, _ in self._sends:
+            w.wait()
+        self._sends = []
+
+    # ---- slots ----------------------------------------------------------------------------------
     def advance(self, n_slots: int) -> None:
-        W, r = self.world, self.rank
+        W, r, M = self.world, self.rank, self.M
+        hop = self.peer_hop
         for _ in range(n_slots):
             t = self.slot
+            u = self._unit(r, t)
+            if hop is None and W > 1:
+                self._post_recv(t + 1)  # sits on the link while this slot computes
             y = None
-            if self._computes(r, t):
-                u = t - r
-                m, s = u % W, u // W
-                from_peer = self.peer_hop is not None and not (r == 0 and s == 0)
-                x = self.first_input(m) if (r == 0 and s == 0) else (self.peer_hop.recv() if from_peer else self.inbox)
-                y = self.stage_fn(u, m, s, x)
-                if from_peer:
-                    self.peer_hop.release()
+            if u is not None:
+                m, s = u % M, u // M
+                from_hop = self._from_hop(t)
+                if not from_hop:
+                    x = self.first_input(m) if s == 0 else self._carry.pop(m)
+                elif hop is not None:
+                    x = hop.recv()
+                else:
+                    x = self._take_recv(t)
+                sends = self._sends_after(t)
+                if self.direct and sends:
+                    y = self.stage_fn(u, m, s, x, out=hop.send_buffer())
+                else:
+                    y = self.stage_fn(u, m, s, x)
+                if from_hop and hop is not None:
+                    hop.release()
                 if r == W - 1:
                     self.completed.append((m, s))
                     self.last_output = y
-            if W > 1 and self.peer_hop is not None:
-                # same send condition as below; the matching receive happens where the message is used
-                if y is not None and (r < W - 1 or t + 1 < self.units):
-                    self.peer_hop.send(y)
-            elif W > 1:
-                nxt, prv = (r + 1) % W, (r - 1) % W
-                # what rank r+1 computes in slot t+1 is the unit rank r computed in slot t;
-                # rank 0 needs the last rank's output only while token steps remain
-                send = y is not None and (r < W - 1 or t + 1 < self.units)
-                recv = self._computes(prv, t) and (r > 0 or t + 1 < self.units) and self._computes(r, t + 1)
-                p2p = []
-                buf = None
-                if send:
-                    p2p.append(self.dist.P2POp(self.dist.isend, y, nxt, self.group))
-                if recv:
-                    if self.recv_spec is not None:
-                        shape, dtype, device = self.recv_spec(t + 1 - r)
-                        buf = torch.empty(shape, dtype=dtype, device=device)
+                if self._like is None:
+                    self._like = x
+                if sends:
+                    if hop is None:
+                        self._send(y)
+                    elif self.direct:
+                        hop.commit(y)
                     else:
-                        like = y if y is not None else (self.inbox if self.inbox is not None else self.first_input(0))
-                        buf = torch.empty_like(like)
-                    p2p.append(self.dist.P2POp(self.dist.irecv, buf, prv, self.group))
-                if p2p:
-                    for req in self.dist.batch_isend_irecv(p2p):
-                        req.wait()
-                self.inbox = buf
-            else:
-                self.inbox = y
+                        hop.send(y)
+                elif W == 1:
+                    self._carry[m] = y
             self.slot += 1
 
 
@@ -363,11 +445,14 @@ class MicroBatchProcessor:
         """prepare (grow caches, descriptors, plan) -> start the region swap for the
         neighbours on the side streams -> run the layers (processor.py:107-146)."""
         batch = self._batch(task_ids, xs)
-        batch.prepare()
+        with phase("alloc+descriptors+plan"):
+            batch.prepare()
         pool = self.kvcache_manager.virtual_page_pool
         if pool.num_pages_swap > 0:
-            pool.swap2(next_group.pinned_memory, prev_group.pinned_memory)
-        return batch.step(self.ignore_eos)
+            with phase("swap2"):
+                pool.swap2(next_group.pinned_memory, prev_group.pinned_memory)
+        with phase("layers"):
+            return batch.step(self.ignore_eos)
 
     def synchronize(self) -> None:
         self.kvcache_manager.synchronize()
@@ -389,12 +474,32 @@ class StageProcessor:
         self.offloaded_kvcaches: dict = {}
         self.current_microbatch_id = 0
 
-    def synchronize(self) -> None:
+    def synchronize(self, host_wait: bool = False) -> None:
+        """The region DMA queued by the previous slot must be over before this slot's
+        kernels touch the region that comes `on`. The reference blocks the host on both
+        DMA streams here (processor.py:226-228); a device-side edge from the DMA streams
+        to the compute stream orders the same things and lets the host run ahead
+        (host_wait=True gives the reference's blocking form). Then flip the regions."""
         pool = self.kvcache_manager.virtual_page_pool
         if pool.stream is not None:
-            pool.stream.synchronize()
-            pool.stream2.synchronize()
+            with phase("swap_wait"):
+                if host_wait:
+                    pool.stream.synchronize()
+                    pool.stream2.synchronize()
+                else:
+                    pool.wait_swap()
         pool.switch()
+
+    def metrics(self) -> dict:
+        """Page accounting of this stage right now (the counterpart of the reference's
+        periodic "avg available pages" log line, processor.py:113-140)."""
+        pool = self.kvcache_manager.virtual_page_pool
+        out_pages, in_pages = pool.last_swap_pages
+        return {"pages_total": pool.num_pages, "pages_main": pool.num_pages_main, "pages_per_region": pool.num_pages_swap,
+                "pages_free": pool.num_avails, "region_on": pool.on, "region_pages_in_flight_out": out_pages,
+                "region_pages_in_flight_in": in_pages,
+                "tasks_resident": sum(len(m.ongoing_paged_kvcaches) for m in self.microbatches),
+                "tasks_offloaded": len(self.offloaded_kvcaches)}
 
     def process_step(self, request: StepRequest) -> tuple:
         mb = self.microbatches[request.microbatch_id]
@@ -410,9 +515,11 @@ class StageProcessor:
         for task_id, seqlen in zip(request.exec_task_ids, request.exec_seqlens):
             self.task_manager.get(task_id).init(seqlen)
         mb.cancel(request.cancel_task_ids)
-        for task_id, h in zip(request.offload_task_ids, mb.offload(request.offload_task_ids)):
-            self.offloaded_kvcaches[task_id] = h
-        mb.reload(request.reload_task_ids, [self.offloaded_kvcaches.pop(t) for t in request.reload_task_ids])
+        if request.offload_task_ids or request.reload_task_ids:
+            with phase("offload+reload"):
+                for task_id, h in zip(request.offload_task_ids, mb.offload(request.offload_task_ids)):
+                    self.offloaded_kvcaches[task_id] = h
+                mb.reload(request.reload_task_ids, [self.offloaded_kvcaches.pop(t) for t in request.reload_task_ids])
         mb.kvcache_manager.synchronize()
         result = None
         if request.exec_task_ids:

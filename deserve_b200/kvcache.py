@@ -332,6 +332,8 @@ class VirtualPagePool(GpuPagePool):
         self.num_pages_main = m
         self.num_pages_swap = s
         self.on = 0
+        self.live_only = True            # swap2 moves only the head of a region that is in use
+        self.last_swap_pages = (0, 0)    # pages per layer the last swap2 moved (out, in)
         if _is_cuda(self.main_device):
             self.stream = torch.cuda.Stream(device=self.main_device)   # outgoing DMA
             self.stream2 = torch.cuda.Stream(device=self.main_device)  # incoming DMA
@@ -369,12 +371,29 @@ class VirtualPagePool(GpuPagePool):
         self.swap_count = from_memory.count
         return self.slices[1 - self.on]
 
+    @staticmethod
+    def _live_pages(free_bitmap) -> int:
+        """Pages of a region that have to travel: everything up to the highest page in
+        use (the allocator hands out the lowest free page first, so the pages in use sit
+        at the head of the region and the tail is free)."""
+        used = np.flatnonzero(~np.asarray(free_bitmap, dtype=bool))
+        return int(used[-1]) + 1 if len(used) else 0
+
     def swap2(self, from_memory: CopiedPinnedMemory, to_memory: CopiedPinnedMemory) -> None:
         """Region `off` -> to_memory, from_memory -> region `off`, asynchronously
         on the two side streams. The outgoing copy first waits for everything
-        already queued on the current stream (the region's last kernels)."""
+        already queued on the current stream (the region's last kernels). Only the
+        head of each region up to its highest page in use travels (`live_only`; the
+        reference moves the whole region whether or not a page of it is in use): the
+        contents of free pages are never read, so leaving them behind changes no
+        result. Set `live_only = False` for the reference's exact byte movement."""
         lo, hi = self._handoff(from_memory, to_memory)
-        self._region_dma(lo, hi, to_memory.memory, from_memory.memory)
+        if self.live_only:
+            n_out, n_in = self._live_pages(to_memory.bitmap), self._live_pages(self._swap_bitmap)
+        else:
+            n_out = n_in = hi - lo
+        self.last_swap_pages = (n_out, n_in)
+        self._region_dma(lo, hi, to_memory.memory, from_memory.memory, n_out, n_in)
 
     def swap(self, from_memory: CopiedPinnedMemory, to_memory: CopiedPinnedMemory) -> None:
         """Same data movement as swap2; the reference's torch statement of it
@@ -385,8 +404,11 @@ class VirtualPagePool(GpuPagePool):
         lo, hi = self.slices[off]
         self._region_dma(lo, hi, to_memory.memory, from_memory.memory)
 
-    def _region_dma(self, lo: int, hi: int, host_out: torch.Tensor, host_in: torch.Tensor) -> None:
+    def _region_dma(self, lo: int, hi: int, host_out: torch.Tensor, host_in: torch.Tensor,
+                    n_out: int | None = None, n_in: int | None = None) -> None:
         _lib.require_cuda(self.pages)
+        n_out = hi - lo if n_out is None else n_out
+        n_in = hi - lo if n_in is None else n_in
         need = self.calc_swap_size()
         for name, t in (("to_memory", host_out), ("from_memory", host_in)):
             if t.numel() * t.element_size() < need * self.pages.element_size():
@@ -397,8 +419,8 @@ class VirtualPagePool(GpuPagePool):
         self.stream2.wait_stream(torch.cuda.current_stream(self.main_device))
         _lib.check(_lib.lib.dsv_region_swap(
             self.pages.data_ptr(), self.num_layers, self.layer_stride_bytes, lo * self.page_bytes,
-            (hi - lo) * self.page_bytes, host_out.data_ptr(), host_in.data_ptr(), self.stream.cuda_stream,
-            self.stream2.cuda_stream, self._edge.cuda_event))
+            (hi - lo) * self.page_bytes, n_out * self.page_bytes, n_in * self.page_bytes, host_out.data_ptr(),
+            host_in.data_ptr(), self.stream.cuda_stream, self.stream2.cuda_stream, self._edge.cuda_event))
 
     def wait_swap(self) -> None:
         """Make the current stream wait for the DMA queued so far (device-side

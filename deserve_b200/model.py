@@ -92,8 +92,11 @@ class LlamaStage:
 
     # ---- one transformer block --------------------------------------------------------------
     def _block(self, w: dict, x: torch.Tensor, ctx: FlashForwardCtx) -> torch.Tensor:
+        """Nine launches plus the attention kernels: norm, fused q|k|v projection, rotary +
+        append, attention, output projection with the residual in its epilogue (addmm), norm,
+        fused gate|up projection, SwiGLU middle, down projection with the residual (addmm)."""
         a, hd = self.model_args, self.model_args.head_dim
-        qkv = rmsnorm(x, w["attn_norm"], a.norm_eps) @ w["wqkv"].t()
+        qkv = torch.mm(rmsnorm(x, w["attn_norm"], a.norm_eps), w["wqkv"].t())
         nq, nkv = a.n_heads * hd, a.n_kv_heads * hd
         q = qkv[:, :nq].unflatten(1, (a.n_heads, hd))
         k = qkv[:, nq : nq + nkv].unflatten(1, (a.n_kv_heads, hd))
@@ -106,10 +109,9 @@ class LlamaStage:
         else:
             assert isinstance(ctx, FlashPrefillCtx)
             attn = ctx.prefill_wrapper.forward(q, pages, causal=True)
-        h = x + attn.view(-1, nq) @ w["wo"].t()
-        gu = rmsnorm(h, w["ffn_norm"], a.norm_eps) @ w["w13"].t()
-        gate, up = gu[:, : a.ffn_dim], gu[:, a.ffn_dim :]
-        return h + (torch.nn.functional.silu(gate) * up) @ w["w2"].t()
+        h = torch.addmm(x, attn.view(-1, nq), w["wo"].t())
+        gu = torch.mm(rmsnorm(h, w["ffn_norm"], a.norm_eps), w["w13"].t())
+        return torch.addmm(h, ops.silu_mul(gu), w["w2"].t())
 
     @torch.inference_mode()
     def forward(self, h: torch.Tensor, ctx: FlashForwardCtx) -> torch.Tensor:

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .pinned import ring as _pinned_ring
+from .pinned import COUNTERS as _COUNTERS, ring as _pinned_ring
 
 _PLAN_HEADER = 8
 
@@ -64,6 +64,7 @@ def append_paged_kv_cache(append_key: torch.Tensor, append_value: torch.Tensor, 
         paged_kv_cache.data_ptr(), page_stride, paged_kv_cache.shape[0], _i32_dev(kv_indices, "kv_indices").data_ptr(),
         _i32_dev(kv_indptr, "kv_indptr").data_ptr(), _i32_dev(kv_last_page_len, "kv_last_page_len").data_ptr(),
         batch, nnz, hkv, d, ps, _lib.dtype_code(paged_kv_cache.dtype), _lib.current_stream_ptr(append_key.device)))
+    _lib.LAUNCHES[0] += 1
 
 
 _INV_FREQ: dict[tuple[int, float], torch.Tensor] = {}
@@ -93,6 +94,7 @@ def apply_rope_inplace(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, o
         q.data_ptr(), k.data_ptr(), qs, ks, _i32_dev(indptr, "indptr").data_ptr(),
         _i32_dev(offsets, "offsets").data_ptr(), offsets.shape[0], q.shape[0], hq, hkv, d, float(rope_theta),
         rope_inv_freq(d, rope_theta).data_ptr(), _lib.dtype_code(q.dtype), _lib.current_stream_ptr(q.device)))
+    _lib.LAUNCHES[0] += 1
 
 
 def apply_rope(q: torch.Tensor, k: torch.Tensor, indptr: torch.Tensor, offsets: torch.Tensor,
@@ -144,6 +146,7 @@ def paged_decode(q: torch.Tensor, paged_kv_cache: torch.Tensor, kv_indices: torc
         kv_last_page_len.data_ptr(), out.data_ptr(), os_, _lib.ptr(lse), plan_host.ctypes.data, plan_dev.data_ptr(),
         _lib.ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(), batch, hq, hkv,
         d, ps, _lib.dtype_code(q.dtype), float(sm_scale), _lib.current_stream_ptr(q.device)))
+    _lib.LAUNCHES[0] += 2 if plan_host[2] > 0 else 1  # the attention kernel, and the merge when requests were split
     return out
 
 
@@ -190,6 +193,7 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise _lib.DeserveKVError(f"workspace_buffer too small: split-KV partials need {ws_bytes} bytes")
         self._ws[: used * 4].view(torch.int32).copy_(pinned[:used], non_blocking=True)
         _pinned_ring("decode_plan").done(slot)
+        _COUNTERS["h2d_bytes"] += used * 4
         self._plan_pinned, self._plan_host = pinned, plan
         self._desc = (indptr, indices, last_page_len, num_qo_heads, num_kv_heads, head_dim, page_size)
 
@@ -248,6 +252,7 @@ def paged_prefill(q: torch.Tensor, qo_indptr: torch.Tensor, paged_kv_cache: torc
         kv_indices.data_ptr(), kv_indptr.data_ptr(), kv_last_page_len.data_ptr(), out.data_ptr(), os_,
         plan_host.ctypes.data, plan_dev.data_ptr(), kv_last_page_len.shape[0], nnz, hq, hkv, d, ps,
         _lib.dtype_code(q.dtype), float(sm_scale), 1 if causal else 0, _lib.current_stream_ptr(q.device)))
+    _lib.LAUNCHES[0] += 1
     return out
 
 
@@ -272,6 +277,9 @@ class BatchPrefillWithPagedKVCacheWrapper:
         if workspace_buffer.dtype != torch.uint8 or workspace_buffer.numel() < self._PLAN_BYTES:
             raise ValueError("workspace_buffer must be a uint8 tensor of at least 1 MiB")
         self._ws = workspace_buffer
+        # head of the workspace that holds the plans and the decode rows' page lists: an eighth of
+        # the buffer, between 1 and 4 MiB (512 decode rows with 8k-token contexts list 266k pages)
+        self._PLAN_BYTES = int(min(4 << 20, max(1 << 20, (workspace_buffer.numel() // 8) & ~0xFFFFF)))
         self._sm_count = _lib.device_info()[0]
         self._plan_host: np.ndarray | None = None
         self._pinned = None
@@ -348,6 +356,7 @@ class BatchPrefillWithPagedKVCacheWrapper:
             self._dec = (o_plan, d_used, o_ip, o_last, o_rows, o_idx, len(dec), int(sub_indptr[-1]), buf[o_plan : o_plan + d_used])
         self._ws[: end * 4].view(torch.int32).copy_(pinned[:end], non_blocking=True)
         _pinned_ring("prefill_plan").done(slot)
+        _COUNTERS["h2d_bytes"] += end * 4
         self._pinned, self._plan_host = pinned, buf
         self._desc = (qo_indptr, paged_kv_indptr, paged_kv_indices, paged_kv_last_page_len, num_qo_heads, head_dim, causal)
 
@@ -398,6 +407,7 @@ def rope_append_paged_kv_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         _i32_dev(kv_last_page_len, "kv_last_page_len").data_ptr(), kv_last_page_len.shape[0], q.shape[0], hq, hkv, d, ps,
         float(rope_theta), rope_inv_freq(d, rope_theta).data_ptr(), _lib.dtype_code(q.dtype),
         _lib.current_stream_ptr(q.device)))
+    _lib.LAUNCHES[0] += 1
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -410,6 +420,22 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out: torch
     _lib.check(_lib.lib.dsv_rmsnorm(x.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr(), x.stride(0),
                                     out.stride(0), x.shape[0], x.shape[1], float(eps), _lib.dtype_code(x.dtype),
                                     _lib.current_stream_ptr(x.device)))
+    _lib.LAUNCHES[0] += 1
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """silu(gate_up[:, :F]) * gate_up[:, F:] for a [rows, 2F] tensor (gate columns, then up columns)."""
+    _lib.require_cuda(gate_up)
+    if gate_up.dim() != 2 or gate_up.stride(1) != 1 or gate_up.shape[1] % 2:
+        raise ValueError("silu_mul: gate_up must be [rows, 2 * ffn_dim] with dense rows")
+    ffn = gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((gate_up.shape[0], ffn), dtype=gate_up.dtype, device=gate_up.device)
+    _lib.check(_lib.lib.dsv_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.stride(0), out.stride(0),
+                                     gate_up.shape[0], ffn, _lib.dtype_code(gate_up.dtype),
+                                     _lib.current_stream_ptr(gate_up.device)))
+    _lib.LAUNCHES[0] += 1
     return out
 
 
@@ -422,4 +448,5 @@ def greedy_sample(logits: torch.Tensor) -> torch.Tensor:
     _lib.check(_lib.lib.dsv_greedy_sample(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1],
                                           out.data_ptr(), _lib.dtype_code(logits.dtype),
                                           _lib.current_stream_ptr(logits.device)))
+    _lib.LAUNCHES[0] += 1
     return out

@@ -50,6 +50,10 @@ class PinnedRing:
 
 _RINGS: dict = {}
 
+# bytes of step metadata queued for upload since the last reset (descriptors, plans, page-id lists):
+# what a benchmark reports as the host->device traffic the API itself causes
+COUNTERS = {"h2d_bytes": 0}
+
 
 def ring(name: str, slots: int = 8, capacity: int = 1 << 14) -> PinnedRing:
     """Process-wide ring by name (one per kind of upload)."""

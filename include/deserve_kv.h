@@ -123,6 +123,17 @@ int dsv_rmsnorm(const void* x, const void* weight, void* out, int64_t x_stride,
                 int64_t out_stride, int rows, int dim, float eps, int dtype, void* stream);
 
 /*
+ * out[r, c] = silu(gate_up[r, c]) * gate_up[r, ffn_dim + c] for c in [0, ffn_dim): the
+ * elementwise middle of the SwiGLU feed-forward, F.silu(self.w1(x)) * self.w3(x) at
+ * deserve_worker/model/layer/linear.py:121-123, on the output of ONE projection whose
+ * rows hold the gate columns followed by the up columns (w1 and w3 stacked). fp32 math;
+ * silu is rounded to dtype and so is the product, like the two torch statements. Row
+ * strides in elements.
+ */
+int dsv_silu_mul(const void* gate_up, void* out, int64_t gate_up_stride, int64_t out_stride,
+                 int rows, int ffn_dim, int dtype, void* stream);
+
+/*
  * Greedy sampling: tokens[r] = argmax of logits[r, 0..vocab), the lowest index
  * among equal maxima. Replaces the per-task torch.argmax + torch.cat loop of
  * deserve_worker/layer_storage.py:219-253 (temperature 0 branch, line 250).
@@ -296,22 +307,27 @@ int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_str
                       void* stream_dma, void** events);
 
 /*
- * Microbatch region swap: for every layer l, copy the slab
- * pages_base + l*layer_stride_bytes + region_offset_bytes (region_bytes long,
- * contiguous) to host_out + l*region_bytes, then fill the same slab from
- * host_in + l*region_bytes. All outgoing copies run on stream_out in layer
- * order; the incoming copy of a group of layers runs on stream_in once that
- * group's outgoing copy has finished (`event`, a cudaEvent_t of the caller,
- * carries the edge), so both directions of the host link are busy at once.
- * This is the data movement VirtualPagePool.swap() states in torch
- * (deserve_worker/kvcache/virtual.py:97-113) and that swap.swap(d, h0, h1,
- * s0, s1, interval) (deserve_worker/kvcache/swap.cpp:9-57, called from
- * virtual.py:79-95) is meant to perform. host_out or host_in may be NULL to
- * skip that direction. Bit-exact. Asynchronous: wait on both streams.
+ * Microbatch region swap: for every layer l, copy the first out_bytes of the slab
+ * pages_base + l*layer_stride_bytes + region_offset_bytes (the region is
+ * region_bytes long, contiguous) to host_out + l*region_bytes, then fill the
+ * first in_bytes of the same slab from host_in + l*region_bytes. out_bytes =
+ * in_bytes = region_bytes moves the whole region, which is the data movement
+ * VirtualPagePool.swap() states in torch (deserve_worker/kvcache/virtual.py:97-113)
+ * and that swap.swap(d, h0, h1, s0, s1, interval)
+ * (deserve_worker/kvcache/swap.cpp:9-57, called from virtual.py:79-95) is meant
+ * to perform. Smaller values move only the head of the region: the allocator
+ * hands out the lowest free page first, so the pages in use sit at the head and a
+ * caller that knows the highest page in use (from the region's bitmap) need not
+ * move the free tail. All outgoing copies run on stream_out in layer order; the
+ * incoming copy of a group of layers runs on stream_in once that group's outgoing
+ * copy has finished (`event`, a cudaEvent_t of the caller, carries the edge), so
+ * both directions of the host link are busy at once. host_out or host_in may be
+ * NULL to skip that direction. Bit-exact. Asynchronous: wait on both streams.
  */
 int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes,
-                    int64_t region_offset_bytes, int64_t region_bytes, void* host_out,
-                    const void* host_in, void* stream_out, void* stream_in, void* event);
+                    int64_t region_offset_bytes, int64_t region_bytes, int64_t out_bytes,
+                    int64_t in_bytes, void* host_out, const void* host_in, void* stream_out,
+                    void* stream_in, void* event);
 
 /*
  * The host half of a step in one native call (no CUDA): for every request of

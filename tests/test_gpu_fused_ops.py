@@ -94,3 +94,22 @@ def test_greedy_sample(dtype, rows, vocab):
     want = kv_math.greedy_tokens(logits)
     assert got.dtype == torch.int32
     assert torch.equal(got[1:], want[1:]) and int(got[0]) == lo
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1.0 / 128), (torch.float16, 1.0 / 1024)])
+@pytest.mark.parametrize("rows,ffn", [(5, 1024), (128, 28672), (1, 8)])
+def test_silu_mul(dtype, tol, rows, ffn):
+    """The SwiGLU middle on a fused gate|up projection output against the reference's two torch
+    statements (deserve_worker/model/layer/linear.py:121-123) on the CPU: at most one rounding step
+    of the output type apart (the silu itself is evaluated by another exp)."""
+    g = torch.Generator().manual_seed(rows + ffn)
+    gu = (torch.randn(rows, 2 * ffn, generator=g) * 2).to(dtype)
+    want = torch.nn.functional.silu(gu[:, :ffn].float()).to(dtype).float() * gu[:, ffn:].float()
+    got = dk.ops.silu_mul(gu.to(DEV)).cpu().float()
+    assert got.shape == (rows, ffn)
+    assert ((got - want).abs() <= 2 * tol * want.abs() + 1e-6).all()
+    # a strided input (the gate|up block as a column slice of a wider tensor)
+    wide = torch.zeros(rows, 2 * ffn + 16, dtype=dtype, device=DEV)
+    wide[:, : 2 * ffn] = gu.to(DEV)
+    got2 = dk.ops.silu_mul(wide[:, : 2 * ffn]).cpu().float()
+    assert torch.equal(got, got2)

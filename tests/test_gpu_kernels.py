@@ -233,3 +233,36 @@ def test_bounded_wait_gives_up_and_reports():
     assert _lib.read_device_status() == 0
     x = torch.arange(8, device=DEV)
     assert int(x.sum()) == 28                      # the context is still usable
+
+
+@pytest.mark.parametrize("name,batch,lo,hi,hq,hkv", [("llama3-8b decode step", 256, 512, 4096, 32, 8),
+                                                    ("llama3-70b head shape", 128, 512, 768, 64, 8)])
+def test_decode_at_benchmark_size_matches_oracle(name, batch, lo, hi, hq, hkv):
+    """One layer of the benchmark's own decode batch — 256 sequences with contexts U[512, 4096] on a
+    seeded permutation of a 1.25x pool, bf16, the real split-KV plan with its partial-state slots —
+    and the 70B head shape (GQA group 8) at microbatch size 128, against the fp32 oracle."""
+    d, ps, dtype = 128, 16, torch.bfloat16
+    desc, pool_pages = random_descriptors(0, batch, lo, hi, ps)
+    g = torch.Generator().manual_seed(2)
+    pages_cpu = (torch.randn(pool_pages, 2, ps, hkv, d, generator=g) * 0.5).to(dtype)
+    q = torch.randn(batch, hq, d, generator=g).to(dtype)
+    k = (torch.randn(batch, hkv, d, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(batch, hkv, d, generator=g) * 0.5).to(dtype)
+    ws = torch.empty(128 << 20, dtype=torch.uint8, device=DEV)
+    wrapper = dk.BatchDecodeWithPagedKVCacheWrapper(ws)
+    dd = to_device(desc, DEV)
+    pages = pages_cpu.to(DEV)
+    dk.append_paged_kv_cache(k.to(DEV), v.to(DEV), dd["indptr"], pages, dd["kv_page_indices"], dd["kv_page_indptr"],
+                             dd["kv_last_page_lens"])
+    wrapper.begin_forward(dd["kv_page_indptr"], dd["kv_page_indices"], dd["kv_last_page_lens"], hq, hkv, d, ps,
+                          data_type=dtype, indptr_host=desc["kv_page_indptr"])
+    got = wrapper.forward(q.to(DEV), pages).float().cpu()
+    n_items, n_slots = int(wrapper._plan_host[1]), int(wrapper._plan_host[2])
+    wrapper.end_forward()
+    kv_math.append_paged(pages_cpu, k, v, desc, ps)
+    assert torch.equal(pages.cpu().view(torch.uint8), pages_cpu.view(torch.uint8)), "pages differ after the append"
+    want = kv_math.paged_attention(q, pages_cpu, desc, ps, causal=False)
+    err = (got - want).abs().max().item()
+    assert err <= 2e-2, f"{name}: max-abs error {err}"
+    if hi > 2048:
+        assert n_items > batch and n_slots > 0, "the benchmark batch must be split over more items than requests"

@@ -53,6 +53,34 @@ def _check_against_dense(cfg, tokens):
     assert len(bad) <= max(1, tokens.numel() // 20), bad
 
 
+def _cfg_many(concurrent, host_tokens=False):
+    """Four microbatches of five sequences (43 tokens = 3 pages each), `concurrent` of them in flight."""
+    model = dk.ModelArgs(dim=512, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=640, ffn_dim=1024, page_size=16)
+    swap = 12 if concurrent > 1 else 0
+    main = concurrent * 5 * 3 - 8 if swap else concurrent * 5 * 3 + 8  # with swap: eight pages of the last microbatch spill
+    return PipelineConfig(model=model, n_microbatches=4, seqs=5, prompt_len=37, new_tokens=6, prefill_seqs=2,
+                          main_pages=main, swap_pages=swap, output_gain=12.0, seed=4, concurrent=concurrent,
+                          warmup_tokens=2, host_tokens=host_tokens)
+
+
+def test_waves_swap_and_the_host_token_loop_do_not_change_a_token():
+    """The same four microbatches (a) all in flight with the region swap on, (b) in two waves of two,
+    (c) one after the other without swap, (d) one after the other with every step's tokens going
+    through pinned host memory: the generated tokens must be identical, bit for bit."""
+    dev = torch.device("cuda:0")
+    runs = {name: run_stage(0, 1, cfg, dev) for name, cfg in [
+        ("all in flight", _cfg_many(4)), ("two waves", _cfg_many(2)), ("one at a time", _cfg_many(1)),
+        ("host tokens", _cfg_many(1, host_tokens=True))]}
+    base = runs["one at a time"]["tokens"]
+    assert base.shape == (4, 5, 6) and (base > 0).any()
+    for name, res in runs.items():
+        assert torch.equal(res["tokens"], base), name
+        assert res["decode_steps_timed"] == 3 and res["decode_ms"] > 0 and res["prefill_ms"] > 0
+    assert runs["all in flight"]["swap_slots"] > 0 and runs["all in flight"]["swap_pages_out"] > 0, \
+        "with four microbatches in flight live pages must travel through the swap regions"
+    _check_against_dense(_cfg_many(1), base)
+
+
 def test_one_stage_pipeline_matches_dense_model():
     cfg = _cfg(1)
     res = run_stage(0, 1, cfg, torch.device("cuda:0"))
@@ -68,8 +96,10 @@ def _worker(rank, world, port, q):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     res = run_stage(rank, world, _cfg(world), dev, dist)
+    # more microbatches than stages: four in flight on two stages, then two waves of two
+    many = [run_stage(rank, world, _cfg_many(c), dev, dist) for c in (4, 2)]
     if rank == world - 1:
-        q.put(res["tokens"].clone())
+        q.put((res["tokens"].clone(), [m["tokens"].clone() for m in many]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -84,7 +114,7 @@ def test_two_stage_pipeline_matches_one_stage_and_dense():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    tokens2 = q.get(timeout=600)
+    tokens2, many2 = q.get(timeout=600)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -92,3 +122,6 @@ def test_two_stage_pipeline_matches_one_stage_and_dense():
     # microbatch 0 as a one-stage job on one GPU: splitting the layers must not change a token
     res = run_stage(0, 1, _cfg(1), torch.device("cuda:0"))
     assert torch.equal(res["tokens"][0], tokens2[0]), "stage split changed the greedy tokens"
+    one_gpu = run_stage(0, 1, _cfg_many(1), torch.device("cuda:0"))["tokens"]
+    for got in many2:  # four microbatches on two stages, all in flight or in two waves: the one-GPU tokens
+        assert torch.equal(got, one_gpu), "stage split / waves changed the greedy tokens"

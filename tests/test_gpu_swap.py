@@ -27,7 +27,12 @@ def _device_status_clean():
 
 
 @pytest.mark.parametrize("dtype,layers", [(torch.bfloat16, 5), (torch.float16, 1), (torch.float32, 8)])
-def test_region_swap_bit_exact(dtype, layers):
+@pytest.mark.parametrize("whole", [True, False])
+def test_region_swap_bit_exact(dtype, layers, whole):
+    """whole: every byte of the region travels, the reference's statement of the swap
+    (VirtualPagePool.swap(), virtual.py:97-113). Otherwise swap2 moves only the head of each
+    region up to its highest page in use: 2 of 4 pages leave, 3 of 4 arrive, the free tails stay
+    where they are on both sides."""
     main, swap, ps, hkv, d = 6, 4, 16, 2, 64
     pool = dk.VirtualPagePool(layers, main, swap, ps, DEV, dtype, n_kv_heads=hkv, head_dim=d)
     ref = _fill(pool, 1)
@@ -39,8 +44,17 @@ def test_region_swap_bit_exact(dtype, layers):
     prev_mb.memory.zero_()
     want_out = torch.zeros(size, dtype=dtype)
     lo, hi = pool.slices[1 - pool.on]
-    swap_ops.region_swap(ref, lo, hi, want_out, incoming)
-    pool.swap2(next_mb, prev_mb)
+    if whole:
+        swap_ops.region_swap(ref, lo, hi, want_out, incoming)
+        pool.swap(next_mb, prev_mb)
+    else:
+        pool._swap_bitmap[:2] = False                 # the region going out has pages 0 and 1 in use
+        next_mb.bitmap[[0, 2]] = False                # the one coming in pages 0 and 2: its head is 3 pages long
+        shape = (layers, swap, *ref.shape[2:])
+        want_out.view(shape)[:, :2] = ref[:, lo : lo + 2]
+        ref[:, lo : lo + 3] = incoming.view(shape)[:, :3]
+        pool.swap2(next_mb, prev_mb)
+        assert pool.last_swap_pages == (2, 3)
     pool.stream.synchronize()
     pool.stream2.synchronize()
     assert torch.equal(prev_mb.memory.view(torch.uint8), want_out.view(torch.uint8))

@@ -1,5 +1,6 @@
-"""The layer-sharded ring pipeline on CPU: world_size 2 and 3 gloo ranks must
-produce exactly what one rank applying all stages in order produces."""
+"""The layer-sharded ring pipeline on CPU: world_size 2, 3 and 4 gloo ranks (with as
+many microbatches as stages, or more) must produce exactly what one rank applying
+all stages in order produces."""
 import os
 import socket
 import sys
@@ -22,9 +23,9 @@ def _stage_math(rank, m, s, x):
     return x * (1.0 + 0.25 * rank) + (m + 1) + 0.5 * s
 
 
-def _expected(world, steps):
+def _expected(world, steps, mbs=None):
     out = {}
-    for m in range(world):
+    for m in range(mbs or world):
         x = torch.full((4, 3), float(m))
         for s in range(steps):
             for r in range(world):
@@ -62,7 +63,7 @@ class _GlooHop:
             w.wait()
 
 
-def _worker(rank, world, port, steps, split, q):
+def _worker(rank, world, port, steps, split, q, mbs=None):
     sys.path.insert(0, str(ROOT))
     import torch.distributed as dist
 
@@ -78,9 +79,11 @@ def _worker(rank, world, port, steps, split, q):
 
     hop = _GlooHop(dist, rank, world) if split == "hop" else None
     split = [] if split == "hop" else split
-    pipe = RingPipeline(rank, world, stage_fn, lambda m: torch.full((4, 3), float(m)), steps, dist=dist, peer_hop=hop)
+    M = mbs or world
+    pipe = RingPipeline(rank, world, stage_fn, lambda m: torch.full((4, 3), float(m)), steps, dist=dist, peer_hop=hop,
+                        microbatches=M)
     finals = {}
-    total_slots = steps * world + world - 1
+    total_slots = steps * M + world - 1
     done = 0
     for n in split + [total_slots - sum(split)]:  # resume after a pause, like warm-up then timed steps
         before = len(pipe.completed)
@@ -91,32 +94,36 @@ def _worker(rank, world, port, steps, split, q):
                 before = len(pipe.completed)
         done += n
         dist.barrier()
+    pipe.flush()
     if hop is not None:
         hop.close()
         # rank 0 takes its first `world` inputs from first_input, everything else arrives over the hop
-        assert hop.received == hop.released == steps * world - (world if rank == 0 else 0)
-        assert hop.sent == steps * world - (world if rank == world - 1 else 0)
+        assert hop.received == hop.released == steps * M - (M if rank == 0 else 0)
+        assert hop.sent == steps * M - (M if rank == world - 1 else 0)
     q.put((rank, seen, {k: v.tolist() for k, v in finals.items()}))
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,steps,split", [(2, 3, [2]), (3, 2, [3, 1]), (2, 1, []), (3, 3, "hop"), (4, 2, "hop")])
-def test_ring_pipeline_matches_sequential(world, steps, split):
+@pytest.mark.parametrize("world,steps,split,mbs", [(2, 3, [2], None), (3, 2, [3, 1], None), (2, 1, [], None),
+                                                   (3, 3, "hop", None), (4, 2, "hop", None),
+                                                   (2, 3, [5], 4), (3, 2, [4, 3], 5), (2, 2, [], 8)])
+def test_ring_pipeline_matches_sequential(world, steps, split, mbs):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, steps, split, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, steps, split, q, mbs)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    want = _expected(world, steps)
+    M = mbs or world
+    want = _expected(world, steps, M)
     by_rank = {r: (seen, finals) for r, seen, finals in results}
     for r in range(world):
         # every rank runs every (microbatch, step) unit once, in ring order
-        assert by_rank[r][0] == [(u % world, u // world) for u in range(steps * world)]
+        assert by_rank[r][0] == [(u % M, u // M) for u in range(steps * M)]
     finals = by_rank[world - 1][1]
     assert set(finals) == set(want)
     for key, val in want.items():
@@ -130,6 +137,16 @@ def test_single_rank_ring_is_a_plain_loop():
     pipe = RingPipeline(0, 1, lambda u, m, s, x: x + 1, lambda m: torch.zeros(2), 5)
     pipe.advance(5)
     assert pipe.last_output.tolist() == [5.0, 5.0] and pipe.completed == [(0, s) for s in range(5)]
+    # three microbatches on one stage: each one's output is its own next input
+    outs = {}
+    pipe = RingPipeline(0, 1, lambda u, m, s, x: outs.setdefault((m, s), x * 2 + m), lambda m: torch.ones(1), 3,
+                        microbatches=3)
+    pipe.advance(9)
+    for m in range(3):
+        x = 1.0
+        for s in range(3):
+            x = 2 * x + m
+            assert outs[(m, s)].item() == x
 
 
 def _dying_worker(rank, world, port, q):
