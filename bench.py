@@ -543,7 +543,7 @@ def measure_hop(args, rank, world, dev, dist, iters=200):
     y = torch.randn(shape, device=dev).to(torch.bfloat16)
     buf = torch.empty_like(y)
     nxt, prv = (rank + 1) % world, (rank - 1) % world
-    send_g, recv_g = make_ring_links(dist, rank, world)
+    send_g, recv_g = make_ring_links(dist, rank, world, dev)
 
     def nccl_hop():
         r = dist.irecv(buf, prv, group=recv_g)
@@ -736,7 +736,7 @@ def kv_step_bench(args, dk, rank, world, local, dev, dist):
             ok = torch.ones(1, device=dev)
             try:
                 from deserve_b200.peer import PeerHop
-                peer_hop = PeerHop(rank, world, (B, hq, d), torch.bfloat16, dev, dist.group.WORLD)
+                peer_hop = PeerHop(rank, world, (B, hq, d), torch.bfloat16, dev, dist.group.WORLD, depth=3)
             except Exception as exc:  # no peer mapping on this node: every rank must take the same path
                 if args.hop == "peer":
                     raise
@@ -936,10 +936,15 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
                          prompt_len=args.pipe_prompt, new_tokens=new_tokens, prefill_seqs=args.pipe_prefill_seqs,
                          main_pages=sz["main_pages"], swap_pages=sz["swap_pages"], concurrent=sz["concurrent"],
                          warmup_tokens=args.warmup)
+    from deserve_b200 import trace
+
     _lib.LAUNCHES[0] = 0
+    trace.enable_host_timing(True)
     with ClockSampler(local) as clocks:
         res = run_stage(rank, world, cfg, dev, dist if world > 1 else None, stage=stage)
     launches = _lib.LAUNCHES[0]
+    host_phases = {k: round(v["ms"] / max(v["calls"], 1), 4) for k, v in trace.host_totals().items()}
+    trace.enable_host_timing(False)
     tm = torch.tensor([res["prefill_ms"], res["decode_ms"], res["decode_compute_ms"]], device=dev, dtype=torch.float64)
     if world > 1:
         mx = tm.clone()
@@ -995,6 +1000,7 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
                                        "its layers, each read once per microbatch step, over the measured copy "
                                        "bandwidth; the projections are cuBLAS GEMMs"},
             "hop": "none" if world == 1 else "nccl isend/irecv, one communicator per link, receive posted one slot ahead",
+            "host_ms_per_call_rank0": host_phases,
         },
     }
     # ---- the same loop with the tokens going through pinned host memory every step (N = 1) ----

@@ -96,17 +96,41 @@ class KVStage:
         return x
 
 
-def make_ring_links(dist, rank: int, world: int):
+def make_ring_links(dist, rank: int, world: int, device=None):
     """One two-rank process group per directed link r -> (r+1) % world, created in
     the same order on every rank. Returns (group this rank sends on, group it
     receives on). A link carries traffic in one direction only, so a receive
     posted early never sits in front of a send on the same communicator (one
     communicator for the whole ring would need grouped send+recv calls, which tie
-    a stage's send to its neighbour's progress)."""
+    a stage's send to its neighbour's progress).
+
+    With `device` given, one element travels over every link before the function
+    returns. The first point-to-point call on a communicator sets up the connection
+    and blocks the host until the peer makes its first call on the same
+    communicator; the links are therefore opened in the order of their index (a
+    rank opens the lower-numbered of its two links first), which pairs the calls
+    up along the ring instead of leaving two neighbours each waiting in a different
+    link's set-up. Later calls find the connections open and never block the host."""
     if world < 2:
         return None, None
     groups = [dist.new_group([r, (r + 1) % world]) for r in range(world)]
-    return groups[rank], groups[(rank - 1) % world]
+    out_link, in_link = rank, (rank - 1) % world
+    if device is not None:
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        one, got = torch.ones(1, device=device), torch.zeros(1, device=device)
+        works = []
+        for link in sorted({out_link, in_link}):
+            if link == out_link:
+                works.append(dist.isend(one, nxt, group=groups[link]))
+            if link == in_link:
+                works.append(dist.irecv(got, prv, group=groups[link]))
+        for w in works:
+            w.wait()
+        if torch.device(device).type == "cuda":
+            torch.cuda.synchronize(device)
+        if float(got.item()) != 1.0:
+            raise RuntimeError("ring link warm-up: the message from the previous stage did not arrive")
+    return groups[out_link], groups[in_link]
 
 
 class RingPipeline:
@@ -117,9 +141,10 @@ class RingPipeline:
     can run some slots, synchronise, and continue with a full ring.
 
     The hop never blocks the host, and blocks the compute stream only where the data
-    is needed: the receive for slot t+1 is posted before slot t computes, the send
-    of slot t's output is queued behind it, and the compute stream waits for a
-    message right before the kernels that read it. Three transports:
+    is needed: the send of slot t's output is queued behind the slot's kernels and is
+    not waited for, the receive for slot t+1 is posted right after it, and the
+    compute stream waits for a message right before the kernels that read it. Three
+    transports:
       * links=(send_group, recv_group) from make_ring_links: NCCL (or gloo)
         isend / irecv, one communicator per directed link;
       * peer_hop (deserve_b200.peer.PeerHop): the sender stores into the next GPU's
@@ -148,7 +173,8 @@ class RingPipeline:
         self.units = total_steps * self.M
         self.dist = dist
         if world > 1 and peer_hop is None and links is None:
-            links = make_ring_links(dist, rank, world)
+            like = first_input(0)
+            links = make_ring_links(dist, rank, world, like.device if like.is_cuda else None)
         self.send_group, self.recv_group = links if links is not None else (None, None)
         self.slot = 0
         self.last_output: torch.Tensor | None = None
@@ -215,8 +241,6 @@ class RingPipeline:
         for _ in range(n_slots):
             t = self.slot
             u = self._unit(r, t)
-            if hop is None and W > 1:
-                self._post_recv(t + 1)  # sits on the link while this slot computes
             y = None
             if u is not None:
                 m, s = u % M, u // M
@@ -248,6 +272,19 @@ class RingPipeline:
                         hop.send(y)
                 elif W == 1:
                     self._carry[m] = y
+            if hop is None and W > 1:
+                # Receives are posted right AFTER this slot's work and send have been queued, never before:
+                # a posted receive is a kernel that spins until the peer's send arrives, and any call on the
+                # host that implicitly waits for the device (a pinned allocation, a lazily loaded kernel
+                # module, a cudaFree) then waits for it. Posted here, a receive only ever depends on work
+                # its peers queued for EARLIER slots, so such a wait always ends; posted before this slot's
+                # own work, two neighbours could wait for each other's current slot forever.
+                # The first stage consumes the last stage's output M - W + 1 slots after it was sent and
+                # posts that far ahead, so that every send has its receive whenever all ranks have run the
+                # same number of slots (a send completes only once its receive is posted, and callers
+                # synchronise the device at such points).
+                for ahead in range(1, (M - W + 1 if r == 0 else 1) + 1):
+                    self._post_recv(t + ahead)
             self.slot += 1
 
 

@@ -260,6 +260,11 @@ class PagedKVCache:
         self.page_table = page_table
         self.pool = pool
 
+    def __class_getitem__(cls, item):
+        # the reference declares the class generic in its pool type and its callers write
+        # PagedKVCache[GpuPagePool] in casts that are evaluated at run time (exec.py, processor.py)
+        return cls
+
     @staticmethod
     def empty(allocator: PageTableAllocator, pool: PagePool) -> "PagedKVCache":
         return PagedKVCache(allocator.alloc(), pool)
@@ -289,6 +294,13 @@ class PinnedMemory:
     def __init__(self, size: int, dtype: torch.dtype = torch.float16) -> None:
         self.size = 0
         self.memory = torch.empty((size,), dtype=dtype, pin_memory=torch.cuda.is_available())
+
+
+class PinnedKVCache:
+    """A range of a PinnedMemory (reference: pinned/kvcache.py:4-8; nothing on the path uses it)."""
+
+    def __init__(self, memory: PinnedMemory, ptr: int, size: int):
+        self.memory, self.ptr, self.size = memory, ptr, size
 
 
 class CopiedPinnedMemory(PinnedMemory):

@@ -154,7 +154,7 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
     if barrier is None:
         barrier = dist.barrier if (dist is not None and world > 1) else (lambda: None)
     if world > 1 and links is None:
-        links = make_ring_links(dist, rank, world)
+        links = make_ring_links(dist, rank, world, device)
     host_ring = ([torch.empty(max(S, 1), dtype=torch.int32, pin_memory=True) for _ in range(Mw + 2)]
                  if cfg.host_tokens else None)
     stats = {"prefill_ms": 0.0, "decode_ms": 0.0, "decode_compute_ms": 0.0, "pages_free_min": pool.num_avails,

@@ -107,10 +107,15 @@ def test_ring_over_peer_memory_matches_sequential():
     procs = [ctx.Process(target=_worker, args=(r, world, port, steps, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        results = [q.get(timeout=240) for _ in procs]
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:  # a worker that is still here hangs: do not leave it behind
+            if p.is_alive():
+                p.kill()
     assert all(status == 0 for _, status, _ in results), results
     finals = {r: f for r, _, f in results}[world - 1]
     for m in range(world):

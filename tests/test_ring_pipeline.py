@@ -189,3 +189,86 @@ def test_a_rank_that_leaves_surfaces_as_an_error_not_a_hang():
     assert got[1] == "left"
     assert got[0].startswith("error after"), got[0]
     assert float(got[0].split()[2][:-2]) < 30.0
+
+
+class _FakeWork:
+    def __init__(self, fn=None):
+        self._fn, self._done = fn, fn is None
+
+    def wait(self):
+        if not self._done:
+            self._fn()
+            self._done = True
+
+    def is_completed(self):
+        return True
+
+
+class _RendezvousLinks:
+    """All ranks of a ring in ONE process, advanced slot by slot in rank order, over links that
+    behave like NCCL point-to-point: a send completes only when its receive has been posted. The
+    fake keeps, per directed link, the messages sent and the receives posted, so a test can ask
+    after any slot whether a send is still waiting for its receive (a device synchronisation at
+    that point would then never return)."""
+
+    def __init__(self, world):
+        self.sent = {(r, (r + 1) % world): [] for r in range(world)}
+        self.posted = {k: 0 for k in self.sent}
+        self.taken = {k: 0 for k in self.sent}
+
+    def for_rank(self, rank):
+        links = self
+
+        class _Dist:
+            def isend(self, t, dst, group=None):
+                links.sent[(rank, dst)].append(t.clone())
+                return _FakeWork()
+
+            def irecv(self, buf, src, group=None):
+                key = (src, rank)
+                links.posted[key] += 1
+                index = links.posted[key] - 1
+
+                def deliver():
+                    assert index < len(links.sent[key]), "the receiver would block: nothing was sent yet"
+                    assert index == links.taken[key], "receives completed out of order"
+                    buf.copy_(links.sent[key][index])
+                    links.taken[key] += 1
+
+                return _FakeWork(deliver)
+
+        return _Dist()
+
+    def unmatched_sends(self):
+        return {k: len(v) - self.posted[k] for k, v in self.sent.items() if len(v) > self.posted[k]}
+
+
+@pytest.mark.parametrize("world,mbs,steps", [(2, 2, 3), (2, 4, 3), (2, 8, 2), (4, 8, 2), (3, 5, 3), (8, 8, 2)])
+def test_no_send_is_left_without_a_posted_receive_at_any_slot_boundary(world, mbs, steps):
+    """With more microbatches than stages the first stage consumes the last stage's output several
+    slots after it was sent; every such send must already have its receive posted when all ranks
+    have run the same number of slots, because the benchmark synchronises the device there."""
+    sys.path.insert(0, str(ROOT))
+    from deserve_b200.engine import RingPipeline
+
+    links = _RendezvousLinks(world)
+    finals = {}
+
+    def make(rank):
+        def stage_fn(u, m, s, x):
+            y = _stage_math(rank, m, s, x)
+            if rank == world - 1:
+                finals[(m, s)] = y.clone()
+            return y
+        return RingPipeline(rank, world, stage_fn, lambda m: torch.full((4, 3), float(m)), steps, dist=links.for_rank(rank),
+                            microbatches=mbs, links=("send", "recv"))
+
+    pipes = [make(r) for r in range(world)]
+    for slot in range(steps * mbs + world - 1):
+        for p in pipes:
+            p.advance(1)
+        assert not links.unmatched_sends(), (slot, links.unmatched_sends())
+    want = _expected(world, steps, mbs)
+    assert set(finals) == set(want)
+    for key, val in want.items():
+        assert finals[key].equal(val), key
