@@ -68,7 +68,10 @@ def parse_args():
                     help="generated tokens per sequence the pools are sized for (the configuration's 256)")
     ap.add_argument("--pipe-kv-budget-gb", type=float, default=0.0,
                     help="HBM for a stage's KV pool; 0 = what is free after the weights minus a reserve")
-    ap.add_argument("--pipe-swap", default="auto", choices=["auto", "off"])
+    ap.add_argument("--pipe-swap", default="auto", choices=["auto", "off", "zero"],
+                    help="auto = region swap on when two or more microbatches are in flight; off = no swap regions; "
+                         "zero = regions exist and rotate but the main pages hold everything, so nothing live travels "
+                         "(isolates the cost of the swap calls from the cost of the bytes)")
     # shape overrides of the KV step for small profiling captures; the defaults are the benchmark
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--batch", type=int, default=256)
@@ -929,9 +932,10 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
     new_tokens = 1 + args.warmup + args.steps
     sz = size_pools(model, le - lb, args.pipe_microbatches, args.pipe_seqs, args.pipe_prompt, new_tokens, budget, world,
                     sized_for_tokens=max(args.pipe_sized_for, new_tokens))
-    if args.pipe_swap == "off" and sz["swap_pages"]:
-        sz["main_pages"] += sz["concurrent"] * args.pipe_seqs
-        sz["swap_pages"] = 0
+    if args.pipe_swap in ("off", "zero") and sz["swap_pages"]:
+        sz["main_pages"] += sz["concurrent"] * args.pipe_seqs + 64
+        if args.pipe_swap == "off":
+            sz["swap_pages"] = 0
     cfg = PipelineConfig(model=model, n_microbatches=args.pipe_microbatches, seqs=args.pipe_seqs,
                          prompt_len=args.pipe_prompt, new_tokens=new_tokens, prefill_seqs=args.pipe_prefill_seqs,
                          main_pages=sz["main_pages"], swap_pages=sz["swap_pages"], concurrent=sz["concurrent"],

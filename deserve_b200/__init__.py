@@ -7,13 +7,13 @@ ABI of libdeserve_kv.so (include/deserve_kv.h).
 """
 from .context import FlashDecodeCtx, FlashForwardCtx, FlashPrefillCtx, ForwardCtx, PagedForwardCtx
 from .kvcache import (ChunkHandle, ChunkPool, CopiedPinnedMemory, CpuChunkPool, CpuPagePool, GpuPagePool,
-                      KVCacheManager, PagedKVCache, PagePool, PageTableAllocator, PageTableHandle, PinnedMemory,
-                      VirtualPagedKVCache, VirtualPagePool)
+                      KVCacheManager, KVConfig, PagedKVCache, PagePool, PageTableAllocator, PageTableHandle,
+                      PinnedKVCache, PinnedMemory, VirtualPagedKVCache, VirtualPagePool, check_page_ownership)
 from .ops import (BatchDecodeWithPagedKVCacheWrapper, BatchPrefillWithPagedKVCacheWrapper, append_paged_kv_cache,
                   apply_rope, apply_rope_inplace, greedy_sample, paged_decode, paged_prefill, rmsnorm,
-                  rope_append_paged_kv_cache)
+                  rope_append_paged_kv_cache, silu_mul)
 from .engine import (BatchDecode, BatchPrefill, BatchResult, KVStage, MicroBatchProcessor, RingPipeline, StageProcessor,
-                     StepRequest)
+                     StepRequest, make_ring_links)
 from .model import LlamaStage, ModelArgs
 from .task import SamplingParams, TaskData, TaskManager
 from .request import InitRequest

@@ -15,6 +15,7 @@ stage's activations to its successor.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable, Optional, Sequence
 
@@ -510,6 +511,24 @@ class StageProcessor:
                                                  ignore_eos) for _ in range(num_rounds)]
         self.offloaded_kvcaches: dict = {}
         self.current_microbatch_id = 0
+        # debug mode (DESERVE_CHECK_PAGES=1 or set the attribute): after every step's allocation the page tables
+        # of the stepping microbatch are checked against the allocator's invariants (kvcache.check_page_ownership)
+        self.check_pages = os.environ.get("DESERVE_CHECK_PAGES", "0") == "1"
+
+    def _check_pages(self, mb: "MicroBatchProcessor") -> None:
+        from .kvcache import check_page_ownership
+
+        pool = self.kvcache_manager.virtual_page_pool
+        away = pool.slices[1 - pool.on] if pool.num_pages_swap > 0 else None
+        check_page_ownership(pool, list(mb.ongoing_paged_kvcaches.values()), in_flight=away)
+        # pages of the main area belong to one cache only, whichever microbatch it is in
+        main_only = []
+        for other in self.microbatches:
+            for kv in other.ongoing_paged_kvcaches.values():
+                ids = kv.page_table.retrieve_np()
+                main_only.extend(ids[ids < pool.num_pages_main].tolist())
+        if len(main_only) != len(set(main_only)):
+            raise AssertionError("a page of the main area is owned by two caches")
 
     def synchronize(self, host_wait: bool = False) -> None:
         """The region DMA queued by the previous slot must be over before this slot's
@@ -562,6 +581,8 @@ class StageProcessor:
         if request.exec_task_ids:
             mb.join([t for t in request.init_tasks if t not in mb.ongoing_paged_kvcaches])
             result = mb.step(request.exec_task_ids, request.xs, prev_mb, next_mb)
+            if self.check_pages:
+                self._check_pages(mb)
             for task_id in request.exec_task_ids:
                 self.task_manager.get(task_id).step()
             if self.layer_storage.need_sample:

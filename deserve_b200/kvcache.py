@@ -701,3 +701,71 @@ class KVCacheManager:
             return
         torch.cuda.current_stream(self.virtual_page_pool.main_device).wait_stream(self.stream)
         self.dma_stream.synchronize()
+
+
+# --------------------------------------------------------------------------
+# one-object configuration, and the page-ownership check
+# --------------------------------------------------------------------------
+@dataclass
+class KVConfig:
+    """Everything that sizes a stage's KV cache in one place. The reference spreads
+    these over its worker's command line (deserve_worker/worker_api.py:131-147:
+    num-main-pages, num-swap-pages, buddy-height, batch-size, num-rounds) and over
+    constants inside the constructors (8 kv heads x 128, page_pool.py:26; context
+    4096, engine/pipeline/processor.py:74). build() calls the same constructors a
+    maintainer would call by hand."""
+
+    num_layers: int
+    n_q_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    page_size: int = 16
+    dtype: torch.dtype = torch.bfloat16
+    num_pages_main: int = 1024
+    num_pages_swap: int = 0
+    max_requests: int = 256
+    max_context_len: int = 4096
+    buddy_height: int = 8
+
+    def pool_bytes(self) -> int:
+        elem = torch.empty(0, dtype=self.dtype).element_size()
+        return (self.num_layers * (self.num_pages_main + 2 * self.num_pages_swap) * 2 * self.page_size
+                * self.n_kv_heads * self.head_dim * elem)
+
+    def build(self, device) -> tuple:
+        """(pool, page table allocator, chunk pool, manager) on `device`."""
+        pool = VirtualPagePool(self.num_layers, self.num_pages_main, self.num_pages_swap, self.page_size,
+                               torch.device(device), self.dtype, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim)
+        tables = PageTableAllocator(self.max_requests, self.max_context_len, self.page_size, torch.device(device))
+        chunks = CpuChunkPool(self.num_layers, self.buddy_height, self.page_size, self.dtype,
+                              n_kv_heads=self.n_kv_heads, head_dim=self.head_dim)
+        return pool, tables, chunks, KVCacheManager(pool, chunks, tables)
+
+
+def check_page_ownership(pool: PagePool, caches: Sequence[PagedKVCache], in_flight: Optional[tuple] = None) -> None:
+    """Debug check of the allocator's invariants over the caches that are live right
+    now (the reference has no such check): no page id appears in two page tables
+    or twice in one; every id lies inside the pool; no owned page is marked free
+    in the bitmap or waits in the prefetch buffer; and, for a virtual pool, no
+    table of these caches points into `in_flight` = (lo, hi), the region that is
+    travelling to or from the host (pass pool.slices[1 - pool.on] for the caches
+    of the microbatch that is about to compute). Raises AssertionError naming the
+    first offending page. Host arithmetic only."""
+    seen: dict = {}
+    buffered = set(pool._buffer.tolist())
+    for c, kv in enumerate(caches):
+        ids = kv.page_table.retrieve_np()
+        for j, pid in enumerate(ids.tolist()):
+            if not 0 <= pid < pool.num_pages:
+                raise AssertionError(f"cache {c} entry {j}: page id {pid} outside the pool of {pool.num_pages}")
+            if pid in seen:
+                raise AssertionError(f"page {pid} is owned twice: cache {seen[pid][0]} entry {seen[pid][1]} and "
+                                     f"cache {c} entry {j}")
+            seen[pid] = (c, j)
+            if pool._bitmap[pid]:
+                raise AssertionError(f"cache {c} entry {j}: page {pid} is marked free in the bitmap")
+            if pid in buffered:
+                raise AssertionError(f"cache {c} entry {j}: page {pid} also waits in the prefetch buffer")
+            if in_flight is not None and in_flight[0] <= pid < in_flight[1]:
+                raise AssertionError(f"cache {c} entry {j}: page {pid} lies in the region [{in_flight[0]}, "
+                                     f"{in_flight[1]}) that is in flight")

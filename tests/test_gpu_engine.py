@@ -36,6 +36,7 @@ def _setup(dtype, rounds, main_pages, swap_pages):
 def test_engine_greedy_tokens_match_dense_reference(dtype):
     rounds, chunk, steps = 3, 48, 10
     args, proc, ref, pool = _setup(dtype, rounds, main_pages=24, swap_pages=12)
+    proc.check_pages = True  # every step: no page in two tables, none in the region that is away
     g = torch.Generator().manual_seed(11)
     prompts = {}
     for mb in range(rounds):

@@ -283,3 +283,33 @@ def test_pinned_ring_hands_out_buffers_round_robin_and_grows():
     r.done(sa)
     a2, sa2 = r.take(2)
     assert sa2 == 0 and a2.data_ptr() == a.data_ptr()
+
+
+def test_kvconfig_builds_the_stage_objects_and_ownership_check_finds_planted_faults():
+    cfg = dk.KVConfig(num_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=8, page_size=4, dtype=torch.float32,
+                      num_pages_main=10, num_pages_swap=3, max_requests=4, max_context_len=64, buddy_height=3)
+    assert cfg.pool_bytes() == 2 * 16 * 2 * 4 * 2 * 8 * 4
+    pool, tables, chunks, mgr = cfg.build("cpu")
+    assert pool.pages.shape == (2, 16, 2, 4, 2, 8) and pool.num_pages_swap == 3 and mgr.virtual_page_pool is pool
+    a, b = dk.VirtualPagedKVCache.empty(tables, pool), dk.VirtualPagedKVCache.empty(tables, pool)
+    a.extend(17)   # 5 pages
+    b.extend(30)   # 8 pages: the main area runs out, the last ones come from the active region
+    assert int(b.isswap.sum()) + int(a.isswap.sum()) == 3
+    dk.check_page_ownership(pool, [a, b])
+    with pytest.raises(AssertionError, match="in flight"):      # the caches do own pages of region 0 ...
+        dk.check_page_ownership(pool, [a, b], in_flight=pool.slices[0])
+    dk.check_page_ownership(pool, [a, b], in_flight=pool.slices[1])  # ... and none of region 1
+    stolen = int(a.page_table.retrieve_np()[2])
+    b.page_table.retrieve_np()[0] = stolen                          # plant: one page in two tables
+    with pytest.raises(AssertionError, match="owned twice"):
+        dk.check_page_ownership(pool, [a, b])
+    b.page_table.retrieve_np()[0] = 99                               # plant: an id outside the pool
+    with pytest.raises(AssertionError, match="outside the pool"):
+        dk.check_page_ownership(pool, [a, b])
+    b.page_table.retrieve_np()[0] = 15                               # plant: a page of the region that is away
+    with pytest.raises(AssertionError, match="in flight"):
+        dk.check_page_ownership(pool, [b], in_flight=pool.slices[1 - pool.on])
+    b.page_table.retrieve_np()[0] = 5
+    b.pool._bitmap[5] = True                                         # plant: an owned page marked free
+    with pytest.raises(AssertionError, match="marked free"):
+        dk.check_page_ownership(pool, [b])
