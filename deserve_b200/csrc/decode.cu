@@ -501,7 +501,57 @@ int dsv_decode_plan(const int32_t* kv_indptr_host, int batch, int n_q_heads, int
     const int mid = lo + (hi - lo) / 2;
     if (count_items(mid) <= target_items) hi = mid; else lo = mid + 1;
   }
-  const int chunk = lo;
+  int chunk = lo;
+  // Small batches (a 128-sequence microbatch with contexts of a few hundred tokens streams
+  // ~0.3 GB per launch): the rule above cuts every request into several short items, and then the
+  // fixed cost of an item (tensor-map fetch, q load, ring fill and drain, partial-state write) and
+  // the extra merge launch weigh as much as the streaming itself. For such launches a few longer
+  // chunk lengths are compared on a model of the launch: items handed longest first to sm_count
+  // CTAs, an item costing its pages plus a fixed overhead, a merge costing a fixed amount when any
+  // request is split. The rule's choice stays unless a candidate is predicted to be clearly faster.
+  if (total_pages <= (int64_t)96 * sm_count && batch > 0) {
+    const int64_t page_bytes = (int64_t)2 * page_size * n_kv_heads * head_dim * elem_size(dtype);
+    const double ovh = std::max<double>(1.0, (512.0 * 1024.0) / (double)page_bytes);  // ~0.5 MB of streaming time
+    const double merge_cost = 1.5 * ovh;
+    std::vector<int> lens;
+    auto predicted = [&](int c) {
+      lens.clear();
+      bool split = false;
+      for (int i = 0; i < batch; ++i) {
+        const int np = kv_indptr_host[i + 1] - kv_indptr_host[i];
+        const int parts = std::max(1, (np + c - 1) / c);
+        split = split || parts > 1;
+        const int base = np / parts, extra = np % parts;
+        for (int p = 0; p < parts; ++p) lens.push_back(base + (p < extra ? 1 : 0));
+      }
+      std::sort(lens.begin(), lens.end(), std::greater<int>());
+      double makespan = 0.0;
+      if ((int)lens.size() <= sm_count) {
+        makespan = lens.empty() ? 0.0 : lens[0] + ovh;
+      } else {
+        std::vector<double> busy(sm_count);  // min-heap of the times at which a CTA slot becomes free
+        for (int k = 0; k < sm_count; ++k) busy[k] = lens[k] + ovh;
+        std::make_heap(busy.begin(), busy.end(), std::greater<double>());
+        for (size_t k = sm_count; k < lens.size(); ++k) {
+          std::pop_heap(busy.begin(), busy.end(), std::greater<double>());
+          busy.back() += lens[k] + ovh;
+          std::push_heap(busy.begin(), busy.end(), std::greater<double>());
+        }
+        for (double t : busy) makespan = std::max(makespan, t);
+      }
+      return makespan + (split ? merge_cost : 0.0);
+    };
+    const double base_cost = predicted(chunk);
+    double best_cost = base_cost;
+    int best = chunk;
+    for (int parts = 1; parts <= 4; ++parts) {
+      const int c = std::max(min_chunk, (max_pages + parts - 1) / parts);
+      if (c <= chunk || count_items(c) > target_items) continue;
+      const double cost = predicted(c);
+      if (cost < best_cost) { best_cost = cost; best = c; }
+    }
+    if (best_cost < 0.93 * base_cost) chunk = best;
+  }
   const int64_t n_items = count_items(chunk);
   const int64_t need = kPlanHeader + 4 * n_items + 2 * (int64_t)batch;
   *plan_used_i32 = need;

@@ -366,6 +366,8 @@ class BatchExec:
         if not self.layer_storage.need_sample:
             return BatchResult(result, ids, result, ids, [], {})
         tokens, produced, done = self.layer_storage.sample(result, self.task_datas, ignore_eos)
+        if not done and all(produced):  # plain decode step: every request got a token and goes on
+            return BatchResult(tokens, ids, tokens, list(ids), [], {})
         all_idx = [i for i, p in enumerate(produced) if p]
         on_idx = [i for i in all_idx if ids[i] not in done]
         pick = lambda idx: tokens[torch.as_tensor(idx, dtype=torch.long, device=tokens.device)] if idx else tokens[:0]

@@ -124,8 +124,9 @@ class LlamaStage:
             h = self._block(w, h, ctx)
             ctx.layer_id += 1
         if self.need_sample:
-            last_rows = (ctx.indptr[1:] - 1).long()
-            h = rmsnorm(h[last_rows], self.norm, self.model_args.norm_eps) @ self.output.t()
+            if h.shape[0] != ctx.bsz:  # prompt chunks: only every request's last row is sampled
+                h = h[(ctx.indptr[1:] - 1).long()]
+            h = torch.mm(rmsnorm(h, self.norm, self.model_args.norm_eps), self.output.t())
         return h
 
     @torch.inference_mode()
