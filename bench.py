@@ -936,16 +936,16 @@ def kv_step_bench(args, dk, rank, world, local, dev, dist):
 # ---------------------------------------------------------------------------
 def pipeline_bench(args, dk, rank, world, local, dev, dist):
     from deserve_b200 import _lib
-    from deserve_b200.model import LlamaStage, ModelArgs, llama_3_70b_args
+    from deserve_b200.model import ModelArgs, llama_3_70b_args
     from deserve_b200.pinned import COUNTERS
-    from deserve_b200.pipeline_driver import PipelineConfig, run_stage, size_pools, token_digest
+    from deserve_b200.pipeline_driver import PipelineConfig, make_stage, run_stage, size_pools, token_digest
 
     model = ModelArgs(**{**llama_3_70b_args.__dict__, "n_layers": args.pipe_layers})
     if model.n_layers % world:
         raise SystemExit("--pipe-layers must be divisible by --gpus")
     lb, le = rank * model.n_layers // world, (rank + 1) * model.n_layers // world
     t0 = time.perf_counter()
-    stage = LlamaStage(model, lb, le, dev, torch.bfloat16, first=(rank == 0), last=(rank == world - 1))
+    stage = make_stage(model, rank, world, dev)
     torch.cuda.synchronize()
     init_s = time.perf_counter() - t0
     free, total = torch.cuda.mem_get_info(dev)
@@ -987,14 +987,10 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
     else:
         prefill_ms, decode_ms, compute_ms = float(tm[0]), float(tm[1]), [float(tm[2])]
     M, S, K = cfg.n_microbatches, cfg.seqs, args.steps
-    # the tokens live on the last rank: share their digest
+    # the tokens live on rank 0 (the first stage finishes the split output head)
     digest, tsum = None, 0
-    if rank == world - 1:
+    if rank == 0:
         digest, tsum = token_digest(res["tokens"]), int(res["tokens"].long().sum())
-    if world > 1:
-        obj = [digest, tsum]
-        dist.broadcast_object_list(obj, src=world - 1)
-        digest, tsum = obj
     slots = K * M
     slot_ms = decode_ms / max(slots, 1)
     # per-stage roofline of a decode slot: the stage's weights once + the KV of its layers once, at HBM speed
@@ -1004,7 +1000,8 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
     head_w = 2 * model.vocab_size * model.dim
     ctx_mid = args.pipe_prompt + args.warmup + (K + 1) / 2
     kv_layer = S * ctx_mid * 2 * model.n_kv_heads * model.head_dim * 2
-    worst_stage_bytes = (le - lb) * (layer_w + kv_layer) + head_w  # the last stage also reads the output head
+    # the output head is split between the last and the first stage (one stage: both halves)
+    worst_stage_bytes = (le - lb) * (layer_w + kv_layer) + (head_w if world == 1 else head_w // 2)
     bound_ms = worst_stage_bytes / (pk["hbm_gbs"] * 1e9) * 1e3
     out = {
         "value": M * S * K / (decode_ms * 1e-3) if decode_ms > 0 else 0.0, "ms_per_step": decode_ms / max(K, 1),
@@ -1027,9 +1024,10 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
             "bubble_frac_per_stage": [1.0 - c / decode_ms if decode_ms > 0 else 0.0 for c in compute_ms],
             "stage_roofline": {"bound": "hbm", "bytes_per_slot_worst_stage": worst_stage_bytes,
                                "bound_ms": bound_ms, "frac": bound_ms / slot_ms if slot_ms > 0 else None,
-                               "note": "weights of the stage's layers + the output head on the last stage + the KV of "
-                                       "its layers, each read once per microbatch step, over the measured copy "
-                                       "bandwidth; the projections are cuBLAS GEMMs"},
+                               "note": "weights of the stage's layers + its half of the output head (last and first "
+                                       "stage; both halves on one GPU) + the KV of its layers, each read once per "
+                                       "microbatch step, over the measured copy bandwidth; the projections are cuBLAS "
+                                       "GEMMs"},
             "hop": "none" if world == 1 else "nccl isend/irecv, one communicator per link, receive posted one slot ahead",
             "host_ms_per_call_rank0": host_phases,
         },

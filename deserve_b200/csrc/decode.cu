@@ -544,9 +544,20 @@ int dsv_decode_plan(const int32_t* kv_indptr_host, int batch, int n_q_heads, int
     const double base_cost = predicted(chunk);
     double best_cost = base_cost;
     int best = chunk;
-    for (int parts = 1; parts <= 4; ++parts) {
-      const int c = std::max(min_chunk, (max_pages + parts - 1) / parts);
-      if (c <= chunk || count_items(c) > target_items) continue;
+    // candidates: the longest request in 1..4 parts, and chunk lengths that make the item count about
+    // 1, 2 or 3 per CTA (each a little longer too: the per-request rounding adds items)
+    int cand[4 + 9];
+    int n_cand = 0;
+    for (int parts = 1; parts <= 4; ++parts) cand[n_cand++] = (max_pages + parts - 1) / parts;
+    for (int per_cta = 1; per_cta <= 3; ++per_cta) {
+      const int c = (int)((total_pages + (int64_t)per_cta * sm_count - 1) / ((int64_t)per_cta * sm_count));
+      cand[n_cand++] = c;
+      cand[n_cand++] = c + std::max(1, c / 8);
+      cand[n_cand++] = c + std::max(2, c / 4);
+    }
+    for (int k = 0; k < n_cand; ++k) {
+      const int c = std::max(min_chunk, cand[k]);
+      if (c <= chunk || c > std::max(min_chunk, max_pages) || count_items(c) > target_items) continue;
       const double cost = predicted(c);
       if (cost < best_cost) { best_cost = cost; best = c; }
     }

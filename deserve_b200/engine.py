@@ -160,7 +160,14 @@ class RingPipeline:
     """
 
     def __init__(self, rank: int, world: int, stage_fn, first_input, total_steps: int, group=None, dist=None,
-                 recv_spec=None, peer_hop=None, microbatches: int | None = None, links=None, direct: bool = False):
+                 recv_spec=None, peer_hop=None, microbatches: int | None = None, links=None, direct: bool = False,
+                 send_final: bool = False):
+        # send_final: the last stage also hands on its output of every microbatch's LAST token step; the first
+        # stage does not compute on it but fetches it with take_finals() once all slots have run (a pipeline
+        # whose first stage finishes the last stage's work, e.g. the second half of a split output head)
+        self.send_final = send_final
+        if send_final and peer_hop is not None:
+            raise ValueError("send_final is implemented for the NCCL / gloo links")
         self.recv_spec = recv_spec
         self.peer_hop = peer_hop
         self.direct = direct and peer_hop is not None
@@ -194,22 +201,37 @@ class RingPipeline:
         return self._unit(rank, slot) is not None
 
     def _from_hop(self, slot: int) -> bool:
-        """Does this rank's input of `slot` arrive over the hop?"""
+        """Does a message for this rank's `slot` arrive over the hop? (With send_final the first stage
+        also receives, in the M slots after its last unit, the last stage's final outputs.)"""
+        if self.world == 1:
+            return False
         u = self._unit(self.rank, slot)
-        return u is not None and self.world > 1 and not (self.rank == 0 and u < self.M)
+        if u is None:
+            return self.send_final and self.rank == 0 and self.units <= slot < self.units + self.M
+        return not (self.rank == 0 and u < self.M)
 
     def _sends_after(self, slot: int) -> bool:
         """Is this rank's output of `slot` somebody's input? (The last stage's output of a
-        microbatch's final token step is not.)"""
+        microbatch's final token step is not, unless send_final.)"""
         u = self._unit(self.rank, slot)
-        return u is not None and self.world > 1 and (self.rank < self.world - 1 or u + self.M < self.units)
+        return u is not None and self.world > 1 and (self.rank < self.world - 1 or self.send_final
+                                                      or u + self.M < self.units)
+
+    def take_finals(self) -> list:
+        """First stage, after every slot has run: the last stage's outputs of the final token step, one per
+        microbatch in microbatch order (send_final=True). On one stage: that stage's own last outputs."""
+        if self.world == 1:
+            return [self._carry[m] for m in range(self.M)]
+        if self.rank != 0:
+            return []
+        return [self._take_recv(self.units + m) for m in range(self.M)]
 
     # ---- NCCL / gloo links ---------------------------------------------------------------------
     def _post_recv(self, slot: int) -> None:
         if slot in self._posted or not self._from_hop(slot):
             return
         if self.recv_spec is not None:
-            shape, dtype, device = self.recv_spec(self._unit(self.rank, slot))
+            shape, dtype, device = self.recv_spec(slot - self.rank)  # the unit; >= units for a final output
             buf = torch.empty(shape, dtype=dtype, device=device)
         else:
             buf = torch.empty_like(self._like if self._like is not None else self.first_input(0))
@@ -253,6 +275,8 @@ class RingPipeline:
                 else:
                     x = self._take_recv(t)
                 sends = self._sends_after(t)
+                if W == 1 and s + 1 == self.units // M:
+                    sends = False  # one stage: the final outputs stay in _carry for take_finals()
                 if self.direct and sends:
                     y = self.stage_fn(u, m, s, x, out=hop.send_buffer())
                 else:

@@ -88,7 +88,7 @@ def run_fragmentation(dev: torch.device, policy: str = "prefill_first", n_arriva
         for _ in range(per_iteration):
             if next_arrival < n_arrivals:
                 i = next_arrival
-                planner.add_prompt(f"r{i}", prompts[i].to(dev, non_blocking=True), SamplingParams(max_new_tokens=int(new[i])))
+                planner.add_prompt(f"r{i}", prompts[i].to(dev, non_blocking=True), SamplingParams(max_new_tokens=int(new[i]), max_seq_len=prompt_hi + 256))
                 next_arrival += 1
         for mb in range(rounds):
             req = planner.convert(reqs[mb], free_pages=pool.num_avails)

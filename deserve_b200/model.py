@@ -65,11 +65,23 @@ class LlamaStage:
     tokens, the last one also applies the final norm and the output projection."""
 
     def __init__(self, args: ModelArgs, layer_begin: int, layer_end: int, device, dtype, seed: int = 0,
-                 first: bool | None = None, last: bool | None = None):
+                 first: bool | None = None, last: bool | None = None, split_head: bool = False):
+        """split_head: the output projection is cut in two halves of the vocabulary. The LAST stage
+        applies the final norm, computes the logits of the lower half and their row maxima, and hands
+        on the normed rows together with (max, argmax) of its half (`pack_partial`); the FIRST stage
+        computes the upper half, combines the two (`finish_head`) and embeds the tokens for the next
+        step. In a pipeline whose stages hold equal numbers of layers this halves the extra work of
+        the stage that owns the head (it reads 1 GB of output weights per microbatch step instead of
+        2 GB) at the price of a 2 MiB instead of a 512-byte message on the link back to the first
+        stage. The reference keeps the whole head on the last worker (layer_storage.py:219-253)."""
         self.model_args = args
         self.layer_begin, self.layer_end = layer_begin, layer_end
         self.need_tokenize = layer_begin == 0 if first is None else first
-        self.need_sample = layer_end == args.n_layers if last is None else last
+        is_last = layer_end == args.n_layers if last is None else last
+        self.split_head = split_head
+        self.head_lo = split_head and is_last          # this stage computes the lower half of the head
+        self.need_sample = is_last and not split_head  # with a split head nobody samples inside forward()
+        self.vocab_lo = (args.vocab_size // 2 + 7) // 8 * 8
         self.main_device, self.dtype = torch.device(device), dtype
         a, hd = args, args.head_dim
         qkv_rows = (a.n_heads + 2 * a.n_kv_heads) * hd
@@ -89,6 +101,44 @@ class LlamaStage:
         if self.need_sample:
             self.norm = torch.ones(a.dim, dtype=dtype, device=device)
             self.output = init_weight((a.vocab_size, a.dim), seed * 7919 + 900002, device, dtype)
+        if self.head_lo:
+            self.norm = torch.ones(a.dim, dtype=dtype, device=device)
+            self.output_lo = init_weight((self.vocab_lo, a.dim), seed * 7919 + 900003, device, dtype)
+        if split_head and self.need_tokenize:
+            self.output_hi = init_weight((a.vocab_size - self.vocab_lo, a.dim), seed * 7919 + 900004, device, dtype)
+
+    # ---- the output head in two halves --------------------------------------------------------
+    def _half_argmax(self, hn: torch.Tensor, w: torch.Tensor):
+        logits = torch.mm(hn, w.t())
+        idx = ops.greedy_sample(logits)
+        return logits.gather(1, idx.long().unsqueeze(1)).squeeze(1).float(), idx
+
+    def pack_partial(self, hn: torch.Tensor) -> torch.Tensor:
+        """Last stage: normed rows [n, dim] + (max, argmax) over the lower half of the vocabulary, as ONE
+        uint8 message: n*dim elements, then n float32 maxima, then n int32 indices."""
+        mx, idx = self._half_argmax(hn, self.output_lo)
+        return torch.cat([hn.reshape(-1).view(torch.uint8), mx.view(torch.uint8), idx.view(torch.uint8)])
+
+    def partial_rows(self, packed: torch.Tensor) -> int:
+        return packed.numel() // (self.model_args.dim * packed.new_empty(0, dtype=self.dtype).element_size() + 8)
+
+    @torch.inference_mode()
+    def finish_head(self, packed: torch.Tensor) -> torch.Tensor:
+        """First stage: the upper half of the head on the rows of a pack_partial message, combined with
+        the lower half's (max, argmax): int32 greedy tokens [n], the lowest index among equal maxima
+        (the lower half wins a tie), exactly what an argmax over the whole vocabulary gives."""
+        n, dim = self.partial_rows(packed), self.model_args.dim
+        nb = n * dim * packed.new_empty(0, dtype=self.dtype).element_size()
+        hn = packed[:nb].view(self.dtype).view(n, dim)
+        mx_lo = packed[nb : nb + 4 * n].view(torch.float32)
+        idx_lo = packed[nb + 4 * n : nb + 8 * n].view(torch.int32)
+        mx_hi, idx_hi = self._half_argmax(hn, self.output_hi)
+        return torch.where(mx_hi > mx_lo, idx_hi + self.vocab_lo, idx_lo).to(torch.int32)
+
+    @property
+    def full_output(self) -> torch.Tensor:
+        """The whole output projection [vocab, dim] of a stage that holds both halves (checks only)."""
+        return self.output if not self.split_head else torch.cat([self.output_lo, self.output_hi])
 
     # ---- one transformer block --------------------------------------------------------------
     def _block(self, w: dict, x: torch.Tensor, ctx: FlashForwardCtx) -> torch.Tensor:
@@ -123,10 +173,11 @@ class LlamaStage:
         for w in self.layers:
             h = self._block(w, h, ctx)
             ctx.layer_id += 1
-        if self.need_sample:
+        if self.need_sample or self.head_lo:
             if h.shape[0] != ctx.bsz:  # prompt chunks: only every request's last row is sampled
                 h = h[(ctx.indptr[1:] - 1).long()]
-            h = torch.mm(rmsnorm(h, self.norm, self.model_args.norm_eps), self.output.t())
+            hn = rmsnorm(h, self.norm, self.model_args.norm_eps)
+            h = self.pack_partial(hn) if self.head_lo else torch.mm(hn, self.output.t())
         return h
 
     @torch.inference_mode()

@@ -117,11 +117,26 @@ def size_pools(model: ModelArgs, layers_here: int, n_microbatches: int, seqs: in
             "kv_bytes_per_microbatch": seqs * pages_seq * page_bytes, "pool_bytes": (main + 2 * swap) * page_bytes}
 
 
+def make_stage(model: ModelArgs, rank: int, world: int, device, dtype=torch.bfloat16, seed: int = 0,
+               output_gain: float = 1.0) -> LlamaStage:
+    """This rank's layers of the model, with the output head split between the last and the first stage."""
+    lb, le = rank * model.n_layers // world, (rank + 1) * model.n_layers // world
+    stage = LlamaStage(model, lb, le, device, dtype, seed=seed, first=(rank == 0), last=(rank == world - 1),
+                       split_head=True)
+    if output_gain != 1.0:
+        for name in ("output_lo", "output_hi"):
+            if hasattr(stage, name):
+                getattr(stage, name).mul_(output_gain)
+    return stage
+
+
 def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, dist=None, stage: LlamaStage | None = None,
               links=None, barrier=None) -> dict:
     """Runs this rank's stage for the whole job. Returns timings and page / swap
-    statistics and, on the last rank, the generated tokens
-    [microbatch][sequence][new_tokens].
+    statistics and, on rank 0, the generated tokens
+    [microbatch][sequence][new_tokens]. The output head is split: the last stage
+    hands the first stage the normed rows and its half's (max, argmax), the first
+    stage finishes the tokens when the message arrives (LlamaStage.finish_head).
 
     Timed regions (CUDA events on the compute stream, each bracketed by a device
     synchronisation and `barrier()`): the prefill slots of every wave, and the
@@ -134,9 +149,7 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
     assert not cfg.host_tokens or world == 1, "host_tokens is the one-stage serving loop"
     lb, le = rank * a.n_layers // world, (rank + 1) * a.n_layers // world
     if stage is None:
-        stage = LlamaStage(a, lb, le, device, cfg.dtype, seed=cfg.seed, first=(rank == 0), last=(rank == world - 1))
-        if stage.need_sample and cfg.output_gain != 1.0:
-            stage.output.mul_(cfg.output_gain)
+        stage = make_stage(a, rank, world, device, cfg.dtype, cfg.seed, cfg.output_gain)
     pool = VirtualPagePool(le - lb, cfg.main_pages, cfg.swap_pages, a.page_size, device, cfg.dtype,
                            n_kv_heads=a.n_kv_heads, head_dim=a.head_dim)
     ctx_len = (cfg.prompt_len + cfg.new_tokens + a.page_size) // a.page_size * a.page_size
@@ -155,6 +168,7 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
         barrier = dist.barrier if (dist is not None and world > 1) else (lambda: None)
     if world > 1 and links is None:
         links = make_ring_links(dist, rank, world, device)
+    elem = torch.empty(0, dtype=cfg.dtype).element_size()
     host_ring = ([torch.empty(max(S, 1), dtype=torch.int32, pin_memory=True) for _ in range(Mw + 2)]
                  if cfg.host_tokens else None)
     stats = {"prefill_ms": 0.0, "decode_ms": 0.0, "decode_compute_ms": 0.0, "pages_free_min": pool.num_avails,
@@ -177,21 +191,26 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
     for wave in range(M // Mw):
         ids = [[f"w{wave}m{m}s{i}" for i in range(S)] for m in range(Mw)]
         first_tokens: dict = {m: [] for m in range(Mw)}  # rank 0: first generated tokens as they come back
-        pending = []                                      # last rank: (m, s, tokens) copied out at the end of the wave
+        pending = []                                      # rank 0: (m, step, tokens) copied out at the end of the wave
         slot_events = []
         in_timed = [False]
         n_host = [0]
 
         def stage_fn(u, m, s, x):
-            req = StepRequest(microbatch_id=m, xs=x)
             gm = wave * Mw + m
+            if rank == 0 and s > 0 and x.dtype == torch.uint8:
+                # the last stage's message of step s-1: normed rows + its half of the head; finish the tokens
+                with phase("finish_head"):
+                    x = stage.finish_head(x)
+                pending.append((m, s - 1, x))
+            req = StepRequest(microbatch_id=m, xs=x)
             if s < P:
                 sel = subset(s)
                 req.exec_task_ids = [ids[m][i] for i in sel]
                 req.exec_seqlens = [cfg.prompt_len] * len(sel)
                 req.init_tasks = {ids[m][i]: (cfg.prompt_len, SamplingParams()) for i in sel}
                 if rank == 0:
-                    if s > 0:  # first tokens of the previous subset, back from the last stage
+                    if s > 0:  # first tokens of the previous subset
                         first_tokens[m].append(x if x.is_cuda else x.clone())
                     req.xs = prompts[gm, sel].reshape(-1).to(device, non_blocking=True)
             else:
@@ -207,6 +226,16 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
                 e0.record()
             proc.synchronize()
             _, result = proc.process_step(req)
+            y = result.ongoing_xs  # activations; on the last stage the packed partial head
+            if cfg.host_tokens:
+                with phase("tokens_to_host"):
+                    toks = stage.finish_head(y)  # one stage: finish at once, the client reads the tokens now
+                    h = host_ring[n_host[0] % len(host_ring)][: toks.numel()]
+                    n_host[0] += 1
+                    h.copy_(toks, non_blocking=True)
+                    torch.cuda.current_stream(device).synchronize()
+                pending.append((m, s, h.clone()))
+                y = h  # pinned; stays intact until Mw + 1 further steps have passed
             if in_timed[0]:
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
@@ -218,40 +247,33 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
                     stats["swap_pages_in"] += i_
                     stats["swap_pages_out_max"] = max(stats["swap_pages_out_max"], o)
                     stats["swap_slots"] += 1
-            y = result.ongoing_xs if rank < world - 1 else result.all_xs
-            if cfg.host_tokens:
-                with phase("tokens_to_host"):
-                    h = host_ring[n_host[0] % len(host_ring)][: y.numel()]
-                    n_host[0] += 1
-                    h.copy_(y, non_blocking=True)
-                    torch.cuda.current_stream(device).synchronize()  # the client reads the tokens here
-                y = h  # pinned; stays intact until Mw + 1 further steps have passed
-            if rank == world - 1:
-                pending.append((m, s, y.clone() if cfg.host_tokens else y))
             return y
 
         def recv_spec(u):
             m, s = u % Mw, u // Mw
-            if rank == 0:  # tokens produced by unit (m, s-1)
+            if rank == 0:  # the packed partial head of unit (m, s-1): rows, then float maxima, then int indices
                 n = len(subset(s - 1)) if s - 1 < P else S
-                return (n,), torch.int32, device
+                return (n * (a.dim * elem + 8),), torch.uint8, device
             n = len(subset(s)) * cfg.prompt_len if s < P else S
             return (n, a.dim), cfg.dtype, device
 
         first = lambda m: torch.empty(0, dtype=torch.int32, device=device)
         pipe = RingPipeline(rank, world, stage_fn, first, cfg.steps, dist=dist, recv_spec=recv_spec, microbatches=Mw,
-                            links=links)
+                            links=links, send_final=True)
         stats["prefill_ms"] += timed(lambda: pipe.advance(P * Mw))
         pipe.advance(Wm * Mw)
         in_timed[0] = True
         stats["decode_ms"] += timed(lambda: pipe.advance(K * Mw))
         in_timed[0] = False
         pipe.advance(world - 1)  # the last units of the later stages
+        if not cfg.host_tokens:  # the tokens of the last step: the first stage finishes the last stage's partial heads
+            for m, packed in enumerate(pipe.take_finals()):
+                pending.append((m, cfg.steps - 1, stage.finish_head(packed)))
         pipe.flush()
         torch.cuda.synchronize(device)
         stats["decode_compute_ms"] += sum(e0.elapsed_time(e1) for e0, e1 in slot_events)
         stats["slots_timed"] += len(slot_events)
-        if rank == world - 1:
+        if rank == 0:
             for m, s, toks in pending:
                 toks = toks.cpu()
                 gm = wave * Mw + m
@@ -272,7 +294,7 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
     res["decode_steps_timed"] = K
     res["bubble_frac"] = (1.0 - stats["decode_compute_ms"] / stats["decode_ms"]) if stats["decode_ms"] > 0 else 0.0
     res["stage"] = stage
-    if rank == world - 1:
+    if rank == 0:
         res["tokens"] = out_tokens
     return res
 
@@ -301,7 +323,7 @@ def main() -> None:
     if args.layers:
         model = ModelArgs(**{**model.__dict__, "n_layers": args.layers})
     lb, le = rank * model.n_layers // world, (rank + 1) * model.n_layers // world
-    stage = LlamaStage(model, lb, le, dev, torch.bfloat16, first=(rank == 0), last=(rank == world - 1))
+    stage = make_stage(model, rank, world, dev)
     free, _ = torch.cuda.mem_get_info(dev)
     budget = int(args.kv_budget_gb * 1e9) if args.kv_budget_gb else free - (8 << 30)
     if world > 1:
@@ -318,7 +340,7 @@ def main() -> None:
         t = torch.tensor([res["prefill_ms"], res["decode_ms"]], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res["prefill_ms"], res["decode_ms"] = float(t[0]), float(t[1])
-    if rank == world - 1:
+    if rank == 0:
         n_decode = args.microbatches * args.microbatch_seqs * res["decode_steps_timed"]
         print(json.dumps({
             "workload": f"llama3-{args.model}-shaped pipeline, {model.n_layers} layers on {world} stages, "

@@ -63,7 +63,8 @@ def _plan(n_pages, hq=32, hkv=8, d=128, ps=16, sms=148):
 
 
 @pytest.mark.parametrize("seed,batch,lo,hi", [(0, 256, 32, 256), (1, 4, 7, 19), (2, 1, 4000, 4000), (3, 700, 1, 3),
-                                              (4, 5, 0, 2)])
+                                              (4, 5, 0, 2), (5, 128, 32, 48), (6, 64, 32, 256), (7, 16, 256, 256),
+                                              (8, 130, 20, 90), (9, 300, 5, 9)])
 def test_decode_plan_covers_every_page_once(seed, batch, lo, hi):
     rng = np.random.default_rng(seed)
     n_pages = rng.integers(lo, hi + 1, size=batch)
@@ -87,6 +88,17 @@ def test_decode_plan_covers_every_page_once(seed, batch, lo, hi):
     assert ws == slots * 32 * (128 + 2) * 4
     sizes = items[:, 2] - items[:, 1]
     assert (np.diff(sizes) <= 0).all()  # longest first
+
+
+def test_decode_plan_keeps_a_small_microbatch_unsplit():
+    """128 sequences with 512-768 tokens (the 70B pipeline's microbatch) stream 0.3 GB per launch: one item
+    per request on 128 of the 148 SMs and no merge launch beats three short items per request."""
+    n_pages = (np.random.default_rng(0).integers(512, 769, size=128) + 15) // 16
+    plan, ws = _plan(n_pages, hq=64)
+    assert plan[1] == 128 and plan[2] == 0 and ws == 0 and plan[3] == n_pages.max()
+    # a single long request still spreads over the machine
+    plan, _ = _plan(np.array([2048]))
+    assert plan[1] >= 100
 
 
 def test_decode_plan_balances_the_llama8b_batch():

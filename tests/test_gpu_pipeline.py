@@ -11,7 +11,7 @@ import torch
 import torch.multiprocessing as mp
 
 import deserve_b200 as dk
-from deserve_b200.pipeline_driver import PipelineConfig, make_prompts, run_stage
+from deserve_b200.pipeline_driver import PipelineConfig, make_prompts, make_stage, run_stage
 from oracle.llama_ref import DenseLlama
 
 pytestmark = pytest.mark.gpu
@@ -27,9 +27,8 @@ def _cfg(n_mb):
 
 def _dense_tokens(cfg):
     dev = torch.device("cuda:0")
-    full = dk.LlamaStage(cfg.model, 0, cfg.model.n_layers, dev, cfg.dtype, seed=cfg.seed)
-    full.output.mul_(cfg.output_gain)
-    ref = DenseLlama(cfg.model, full.layers, full.tok_embeddings, full.norm, full.output)
+    full = make_stage(cfg.model, 0, 1, dev, cfg.dtype, cfg.seed, cfg.output_gain)  # both halves of the split head
+    ref = DenseLlama(cfg.model, full.layers, full.tok_embeddings, full.norm, full.full_output)
     prompts = make_prompts(cfg)
     out = torch.zeros(cfg.n_microbatches, cfg.seqs, cfg.new_tokens, dtype=torch.int32)
     gaps = []
@@ -51,6 +50,28 @@ def _check_against_dense(cfg, tokens):
                     want = ref.step(tid, torch.tensor([got], dtype=torch.int32))
     assert all(g < 0.05 for *_, g in bad), bad          # only ties within 16-bit resolution may differ
     assert len(bad) <= max(1, tokens.numel() // 20), bad
+
+
+def test_split_head_gives_the_argmax_over_the_whole_vocabulary():
+    """The last stage's half (max, argmax) + the first stage's half = the argmax over all logits, the lowest
+    index among equal maxima; a maximum that occurs in both halves goes to the lower half."""
+    dev = torch.device("cuda:0")
+    model = dk.ModelArgs(dim=256, n_layers=1, n_heads=4, n_kv_heads=2, vocab_size=1000, ffn_dim=512, page_size=16)
+    st = make_stage(model, 0, 1, dev, torch.bfloat16, seed=1)
+    assert st.output_lo.shape[0] == 504 and st.output_hi.shape[0] == 496 and not st.need_sample
+    st.output_hi[7] = st.output_lo[100] * 3      # rows 0..3 will peak at column 100 and, equally, at 504 + 7
+    st.output_lo[100] *= 3
+    g = torch.Generator(device=dev).manual_seed(0)
+    hn = torch.randn(37, 256, device=dev, generator=g).to(torch.bfloat16)
+    hn[:4] = st.output_lo[100].sign() * 0.5       # aligned with that row: its logit is the maximum
+    packed = st.pack_partial(hn)
+    assert packed.dtype == torch.uint8 and packed.numel() == 37 * (256 * 2 + 8) and st.partial_rows(packed) == 37
+    got = st.finish_head(packed)
+    logits = torch.cat([hn @ st.output_lo.t(), hn @ st.output_hi.t()], dim=1)
+    want = dk.greedy_sample(logits)
+    assert torch.equal(got, want)
+    assert got[:4].tolist() == [100] * 4 and (logits[:4, 100] == logits[:4, 504 + 7]).all()
+    assert (got >= 504).any() and (got < 504).any()
 
 
 def _cfg_many(concurrent, host_tokens=False):
@@ -98,7 +119,7 @@ def _worker(rank, world, port, q):
     res = run_stage(rank, world, _cfg(world), dev, dist)
     # more microbatches than stages: four in flight on two stages, then two waves of two
     many = [run_stage(rank, world, _cfg_many(c), dev, dist) for c in (4, 2)]
-    if rank == world - 1:
+    if rank == 0:  # the first stage finishes the split output head, so the tokens are there
         q.put((res["tokens"].clone(), [m["tokens"].clone() for m in many]))
     dist.barrier()
     dist.destroy_process_group()

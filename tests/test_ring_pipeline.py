@@ -147,6 +147,7 @@ def test_single_rank_ring_is_a_plain_loop():
         for s in range(3):
             x = 2 * x + m
             assert outs[(m, s)].item() == x
+    assert [t.item() for t in pipe.take_finals()] == [outs[(m, 2)].item() for m in range(3)]
 
 
 def _dying_worker(rank, world, port, q):
@@ -243,8 +244,9 @@ class _RendezvousLinks:
         return {k: len(v) - self.posted[k] for k, v in self.sent.items() if len(v) > self.posted[k]}
 
 
+@pytest.mark.parametrize("send_final", [False, True])
 @pytest.mark.parametrize("world,mbs,steps", [(2, 2, 3), (2, 4, 3), (2, 8, 2), (4, 8, 2), (3, 5, 3), (8, 8, 2)])
-def test_no_send_is_left_without_a_posted_receive_at_any_slot_boundary(world, mbs, steps):
+def test_no_send_is_left_without_a_posted_receive_at_any_slot_boundary(world, mbs, steps, send_final):
     """With more microbatches than stages the first stage consumes the last stage's output several
     slots after it was sent; every such send must already have its receive posted when all ranks
     have run the same number of slots, because the benchmark synchronises the device there."""
@@ -261,7 +263,7 @@ def test_no_send_is_left_without_a_posted_receive_at_any_slot_boundary(world, mb
                 finals[(m, s)] = y.clone()
             return y
         return RingPipeline(rank, world, stage_fn, lambda m: torch.full((4, 3), float(m)), steps, dist=links.for_rank(rank),
-                            microbatches=mbs, links=("send", "recv"))
+                            microbatches=mbs, links=("send", "recv"), send_final=send_final)
 
     pipes = [make(r) for r in range(world)]
     for slot in range(steps * mbs + world - 1):
@@ -272,3 +274,7 @@ def test_no_send_is_left_without_a_posted_receive_at_any_slot_boundary(world, mb
     assert set(finals) == set(want)
     for key, val in want.items():
         assert finals[key].equal(val), key
+    if send_final:  # the first stage also gets the last stage's outputs of the final token step
+        got = pipes[0].take_finals()
+        assert len(got) == mbs and all(got[m].equal(want[(m, steps - 1)]) for m in range(mbs))
+        assert all(len(v) == links.taken[k] for k, v in links.sent.items())  # every message was consumed
