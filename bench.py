@@ -105,6 +105,8 @@ def parse_args():
                          "one-layer decode and chunked-prefill inputs; prints its own JSON line")
     ap.add_argument("--no-library", action="store_true",
                     help="N = 1: do not run the flashinfer comparator (a child process, at most 240 s) for the `library` field")
+    ap.add_argument("--frag-policy", default="prefill_first", choices=["vanilla", "prefill_first", "decode_first"],
+                    help="join policy of the first stage's scheduler in the --fragmentation run")
     ap.add_argument("--fragmentation", action="store_true",
                     help="only run the mixed prefill/decode fragmentation workload (512 arrivals, lognormal prompts, "
                          "512-token chunks, 128 decode steps, seeded departures); prints its own JSON line")
@@ -1082,7 +1084,8 @@ def run_ours(args):
         from deserve_b200.fragmentation import run_fragmentation
 
         torch.cuda.set_device(local)
-        print(json.dumps({"fragmentation": run_fragmentation(torch.device("cuda", local))}), flush=True)
+        print(json.dumps({"fragmentation": run_fragmentation(torch.device("cuda", local), policy=args.frag_policy)}),
+              flush=True)
         return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")

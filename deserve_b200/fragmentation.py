@@ -96,6 +96,7 @@ def run_fragmentation(dev: torch.device, policy: str = "prefill_first", n_arriva
             reloads += len(req.reload_task_ids)
             ids = list(req.exec_task_ids)
             seqlens = list(req.exec_seqlens)[: len(ids)]
+            in_prompt = [tm.get(t).start_pos < tm.get(t).initial_seqlen for t in ids]  # before the step
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             proc.synchronize()
@@ -104,19 +105,19 @@ def run_fragmentation(dev: torch.device, policy: str = "prefill_first", n_arriva
             if result is None:
                 continue
             steps += 1
-            rows_prompt = sum(n for n in seqlens if n > 1)
+            rows_prompt = sum(n for n, p in zip(seqlens, in_prompt) if p)
             events.append((e0, e1, rows_prompt, len(result.all_task_ids)))
             prompt_rows += rows_prompt
             generated += len(result.all_task_ids)
             for t in result.all_task_ids:
                 produced[int(t[1:])] += 1
             done.update(result.done_task_ids)
+            free = pool.page_bitmap.numpy().copy()
+            used = ~free
+            reused_total += int((used & prev_free & ever_used).sum())  # taken now, free a step ago, used before
+            ever_used |= used
+            prev_free = free
             if steps % stats_every == 0:
-                free = pool.page_bitmap.numpy().copy()
-                used = ~free
-                reused_total += int((used & prev_free & ever_used).sum())
-                ever_used |= used
-                prev_free = free
                 samples.append({"step": steps, "pages_free": int(pool.num_avails), "longest_free_run": longest_free_run(free),
                                 "pages_reused_so_far": reused_total, "tasks_resident": sum(
                                     len(m.ongoing_paged_kvcaches) for m in proc.microbatches),
