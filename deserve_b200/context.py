@@ -87,6 +87,8 @@ class FlashForwardCtx(PagedForwardCtx):
     kv_page_indices: torch.Tensor
     kv_page_indptr: torch.Tensor
     kv_last_page_lens: torch.Tensor
+    # host copies of the descriptor arrays: views of a pinned buffer that is reused once 15 later steps have
+    # been prepared, i.e. valid for this step (planning, bookkeeping), not to be kept
     host: dict[str, np.ndarray] = field(default_factory=dict, repr=False)
 
     @staticmethod
