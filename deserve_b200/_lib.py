@@ -57,6 +57,9 @@ _SIGNATURES = {
     "dsv_host_build_step": (c_int, [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                     c_int32, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "dsv_device_build_step": (c_int, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int64, c_void_p,
+                                      c_int32, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "dsv_device_free_rows": (c_int, [c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "dsv_append_paged_kv": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "dsv_apply_rope_inplace": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,

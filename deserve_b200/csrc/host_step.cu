@@ -10,6 +10,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "step_core.cuh"
 
 extern "C" {
 
@@ -32,42 +33,17 @@ int dsv_host_build_step(uint8_t* bitmap, int32_t num_pages, int32_t* buffer, int
   for (int i = 0; i < batch; ++i) {
     const int cur = start_pos[i] + seqlen[i];
     const int want_tokens = std::max(cur, initial_seqlen[i]);
-    const int have = occupied[i];
-    if (want_tokens > have * page_size) {
-      const int new_n = (want_tokens + page_size - 1) / page_size;
-      const int size = new_n - have;
-      DSV_REQUIRE(new_n <= table_cols, "host_build_step: request %d needs %d pages, the table row holds %lld", i, new_n,
-                  (long long)table_cols);
-      if (size > *num_avails) {  // the reference's ValueError("Not enough pages")
-        *failed_request = i;
-        *failed_need = size;
-        return DSV_E_WORKSPACE;
-      }
-      *num_avails -= size;
-      if (size > *buffer_len) {  // refill: the lowest free indices, at least fetch_size of them
-        const int want = std::max(fetch_size, size - *buffer_len);
-        if (*buffer_start + *buffer_len + want > buffer_cap) {  // compact the window to the front
-          std::memmove(buffer, buffer + *buffer_start, sizeof(int32_t) * (size_t)*buffer_len);
-          *buffer_start = 0;
-        }
-        int32_t* tail = buffer + *buffer_start + *buffer_len;
-        int got = 0;
-        for (int pg = 0; pg < num_pages && got < want; ++pg)
-          if (bitmap[pg]) {
-            bitmap[pg] = 0;
-            tail[got++] = pg;
-          }
-        *buffer_len += got;
-      }
-      int32_t* row = tables + (int64_t)slot[i] * table_cols;
-      const int32_t* ids = buffer + *buffer_start;
-      for (int k = 0; k < size; ++k) {
-        row[have + k] = ids[k];
-        if (isswap != nullptr) isswap[(int64_t)slot[i] * table_cols + have + k] = ids[k] >= num_pages_main ? 1 : 0;
-      }
-      *buffer_start += size;
-      *buffer_len -= size;
-      occupied[i] = new_n;
+    int32_t need = 0;
+    uint8_t* flags = isswap != nullptr ? isswap + (int64_t)slot[i] * table_cols : nullptr;
+    const int rc = grow_request(bitmap, num_pages, buffer, buffer_cap, buffer_start, buffer_len, num_avails, fetch_size,
+                                page_size, num_pages_main, tables + (int64_t)slot[i] * table_cols, flags, table_cols,
+                                want_tokens, occupied + i, &need);
+    DSV_REQUIRE(rc != GROW_ROW_FULL, "host_build_step: request %d needs %d pages, the table row holds %lld", i, need,
+                (long long)table_cols);
+    if (rc == GROW_NO_PAGES) {
+      *failed_request = i;
+      *failed_need = need;
+      return DSV_E_WORKSPACE;
     }
     total_pages += (cur + page_size - 1) / page_size;
   }

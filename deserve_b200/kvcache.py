@@ -346,6 +346,7 @@ class VirtualPagePool(GpuPagePool):
         self.on = 0
         self.live_only = True            # swap2 moves only the head of a region that is in use
         self.last_swap_pages = (0, 0)    # pages per layer the last swap2 moved (out, in)
+        self.dma_events: list | None = None  # set to [] to collect (out start, out end, in start, in end) timing events
         if _is_cuda(self.main_device):
             self.stream = torch.cuda.Stream(device=self.main_device)   # outgoing DMA
             self.stream2 = torch.cuda.Stream(device=self.main_device)  # incoming DMA
@@ -429,10 +430,19 @@ class VirtualPagePool(GpuPagePool):
                 raise ValueError(f"{name} dtype {t.dtype} differs from the pool dtype {self.main_dtype}")
         self.stream.wait_stream(torch.cuda.current_stream(self.main_device))
         self.stream2.wait_stream(torch.cuda.current_stream(self.main_device))
+        timing = None
+        if self.dma_events is not None and (n_out or n_in):
+            timing = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            timing[0].record(self.stream)
+            timing[2].record(self.stream2)
         _lib.check(_lib.lib.dsv_region_swap(
             self.pages.data_ptr(), self.num_layers, self.layer_stride_bytes, lo * self.page_bytes,
             (hi - lo) * self.page_bytes, n_out * self.page_bytes, n_in * self.page_bytes, host_out.data_ptr(),
             host_in.data_ptr(), self.stream.cuda_stream, self.stream2.cuda_stream, self._edge.cuda_event))
+        if timing is not None:
+            timing[1].record(self.stream)
+            timing[3].record(self.stream2)
+            self.dma_events.append(timing)
 
     def wait_swap(self) -> None:
         """Make the current stream wait for the DMA queued so far (device-side

@@ -29,6 +29,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from . import _lib
 from .engine import RingPipeline, StageProcessor, StepRequest, make_ring_links
 from .kvcache import CpuChunkPool, KVCacheManager, PageTableAllocator, VirtualPagePool
 from .model import LlamaStage, ModelArgs, llama_3_8b_args, llama_3_70b_args
@@ -172,7 +173,8 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
     host_ring = ([torch.empty(max(S, 1), dtype=torch.int32, pin_memory=True) for _ in range(Mw + 2)]
                  if cfg.host_tokens else None)
     stats = {"prefill_ms": 0.0, "decode_ms": 0.0, "decode_compute_ms": 0.0, "pages_free_min": pool.num_avails,
-             "swap_pages_out": 0, "swap_pages_in": 0, "swap_slots": 0, "swap_pages_out_max": 0, "slots_timed": 0}
+             "swap_pages_out": 0, "swap_pages_in": 0, "swap_slots": 0, "swap_pages_out_max": 0, "slots_timed": 0,
+             "launches_timed": 0, "swap_dma_out_ms": 0.0, "swap_dma_in_ms": 0.0, "swap_dma_slots": 0}
 
     def subset(s):
         return list(range(s * c, min(S, (s + 1) * c)))
@@ -263,7 +265,11 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
         stats["prefill_ms"] += timed(lambda: pipe.advance(P * Mw))
         pipe.advance(Wm * Mw)
         in_timed[0] = True
+        if pool.num_pages_swap:
+            pool.dma_events = []
+        launches0 = _lib.LAUNCHES[0]
         stats["decode_ms"] += timed(lambda: pipe.advance(K * Mw))
+        stats["launches_timed"] += _lib.LAUNCHES[0] - launches0  # this package's kernels inside the timed region
         in_timed[0] = False
         pipe.advance(world - 1)  # the last units of the later stages
         if not cfg.host_tokens:  # the tokens of the last step: the first stage finishes the last stage's partial heads
@@ -273,6 +279,11 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
         torch.cuda.synchronize(device)
         stats["decode_compute_ms"] += sum(e0.elapsed_time(e1) for e0, e1 in slot_events)
         stats["slots_timed"] += len(slot_events)
+        if pool.dma_events:  # how long the region DMA of a slot runs on its side streams (both directions overlap)
+            stats["swap_dma_out_ms"] += sum(a.elapsed_time(b) for a, b, _, _ in pool.dma_events)
+            stats["swap_dma_in_ms"] += sum(c.elapsed_time(d) for _, _, c, d in pool.dma_events)
+            stats["swap_dma_slots"] += len(pool.dma_events)
+        pool.dma_events = None
         if rank == 0:
             for m, s, toks in pending:
                 toks = toks.cpu()

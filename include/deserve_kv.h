@@ -357,6 +357,35 @@ int dsv_host_build_step(uint8_t* bitmap, int32_t num_pages, int32_t* buffer, int
                         int32_t* failed_need);
 
 /*
+ * The same step with the allocator state on the DEVICE: bitmap[num_pages] (1 = free),
+ * buffer[num_pages] (prefetched free ids), state (int64[2]: free pages; then the
+ * prefetch window as two int32, start and length), tables[max_requests, table_cols]
+ * and occupied[max_requests] (pages per table row) are device arrays that only these
+ * kernels touch. req is a DEVICE array of batch x 6 int32 per request: table row,
+ * start_pos, seqlen, initial_seqlen, and the two prefix sums the host can compute
+ * from token counts alone (first new-token row, first page-list entry). With grow = 1
+ * one thread first grows the requests in batch order with the very function the host
+ * builder uses (same page ids as deserve_worker/kvcache/paged/page_pool.py:38-55 hands
+ * out); then one CTA per request writes the six descriptor sections of
+ * deserve_worker/model/context/flash.py:29-64 into `out` (device) at
+ * section_offsets_host[0..6) (HOST array, same order as dsv_host_build_step), page
+ * ids copied straight from the table rows. The caller checks the page budget and the
+ * row length on its own counters before the call (it raises the reference's
+ * ValueError itself); a disagreement shows up in the device status word.
+ * dsv_device_free_rows returns the pages of the given table rows (device array of n
+ * row numbers) to the bitmap and empties the rows (PagedKVCache.free,
+ * kvcache.py:31-33; page_pool.py:73-76).
+ */
+int dsv_device_build_step(uint8_t* bitmap, int32_t num_pages, int32_t* buffer, int64_t* state,
+                          int32_t fetch_size, int32_t page_size, int32_t* tables,
+                          int64_t table_cols, int32_t* occupied, int32_t max_requests,
+                          const int32_t* req, int batch, int grow, int32_t* out,
+                          const int64_t* section_offsets_host, void* stream);
+int dsv_device_free_rows(uint8_t* bitmap, int32_t num_pages, int64_t* state, const int32_t* tables,
+                         int64_t table_cols, int32_t* occupied, const int32_t* slots, int n,
+                         void* stream);
+
+/*
  * The hop between pipeline stages over peer memory. The reference posts each
  * microbatch's activations to the next worker over HTTP
  * (deserve_worker/engine/pipeline/processor.py:218-224, PipelineProcessor.send_request);
