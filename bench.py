@@ -251,7 +251,7 @@ def cpu_kv_layer_sample(args, steps, warmup, n_seq=None):
 
 
 def cpu_config1_full():
-    """BASELINE configuration 1 in full on the host: 2 layers, 8 q / 2 kv heads, head_dim 64, fp32, page
+    """The small CPU configuration in full on the host: 2 layers, 8 q / 2 kv heads, head_dim 64, fp32, page
     size 16, 4 sequences with contexts U[100,300] from seed 0, 32 decode steps (allocator, descriptors,
     append, paged attention), all through the oracle."""
     from oracle import kv_math
@@ -1034,7 +1034,8 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
                                        "stage; both halves on one GPU) + the KV of its layers, each read once per "
                                        "microbatch step, over the measured copy bandwidth; the projections are cuBLAS "
                                        "GEMMs"},
-            "hop": "none" if world == 1 else "nccl isend/irecv, one communicator per link, receive posted one slot ahead",
+            "hop": "none" if world == 1 else "nccl isend/irecv, one communicator per directed link; a receive is posted right "
+                   "after the slot's send, the compute stream waits for it only where the next slot reads it",
             "host_ms_per_call_rank0": host_phases,
         },
     }

@@ -5,7 +5,7 @@ TransformerBlock, BatchDecode / BatchPrefill.prepare/step
 offload / reload (deserve_worker/engine/microbatch/processor.py:24-146) run on the
 GPU with this package standing where the reference imports `flashinfer`, its
 `deserve_worker.kvcache.*` modules and `deserve_worker.model.context.flash` — the
-import swaps INTEGRATION.md describes. The activations they produce are compared
+import swaps a maintainer would make. The activations they produce are compared
 with a dense fp32 evaluation of the same blocks.
 
 The reference's sources are not part of this repository: the test runs from a
