@@ -8,7 +8,8 @@ x 128 sequences, each with a 512-token prompt of random ids (vocab 128256),
 greedy decoding; every stage owns the KV pages of its layers and runs the
 reference's per-step order (page allocation, descriptors, rotary + append,
 paged attention, region swap) on them; activations hop between stages over
-NCCL links. A step = one decode token for all 8 x 128 sequences. The same job
+NCCL links; the output head is split between the last and the first stage. A
+step = one decode token for all 8 x 128 sequences. The same job
 runs at every N (strong scaling); `token_sha256` of the generated tokens must be
 the same at every N. On one GPU the 141 GB of weights leave room for one
 microbatch's KV, so the microbatches run one after the other and nothing is
@@ -22,8 +23,9 @@ attention) that the `roofline` of the decode-attention kernel is measured on; on
 N > 1 GPUs its layers are split over the stages and N microbatches rotate (weak
 scaling of the pure KV path). On one GPU the line also carries the chunked-
 prefill kernel (`prefill_kernel`), the KV swap stress (`swap`), the same
-pipeline through host token buffers (`e2e`) and the CPU restatement of the
-reference timed on the host cores (`cpu_baseline`).
+pipeline through host token buffers (`e2e`), the library the reference calls
+on the same tensors (`library`) and the CPU restatement of the reference timed
+on the host cores (`cpu_baseline`).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
