@@ -10,6 +10,8 @@ each (deserve_worker/model/context/flash.py:50-64).
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 
 
@@ -27,10 +29,12 @@ class PinnedRing:
         self._bufs = [torch.empty(capacity, dtype=torch.int32, pin_memory=self._pin) for _ in range(slots)]
         self._events: list = [None] * slots
         self._next = 0
+        self._lock = threading.Lock()  # rings are process-wide: the engine thread and a transfer thread may share one
 
     def take(self, n: int) -> tuple[torch.Tensor, int]:
-        slot = self._next
-        self._next = (slot + 1) % len(self._bufs)
+        with self._lock:
+            slot = self._next
+            self._next = (slot + 1) % len(self._bufs)
         ev = self._events[slot]
         if ev is not None:
             ev.synchronize()  # the copy queued slots steps ago: long done in steady state
