@@ -25,6 +25,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 #include <vector>
 
@@ -37,8 +38,10 @@ constexpr int kBN = 128;                 // kv tokens per tile
 constexpr int kVStages = 3;                // V tiles in flight (K: 2)
 constexpr int kThreads = 352;            // 2 x 4 softmax warps, K producer, MMA warp, V producer
 constexpr int kSpinLimit = 1 << 21;
-constexpr int32_t kPrefillMagic = 0x44535032;  // "DSP2"
-constexpr int kPlanHeader = 8;
+constexpr int32_t kPrefillMagic = 0x44535033;  // "DSP3"
+// plan header: magic, single-CTA items, q tokens per tile, causal, batch, offset of the single-CTA items,
+// q heads, kv heads, pair items, offset of the pair items, 2 unused; then the items, 4 int32 each
+constexpr int kPlanHeader = 12;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
@@ -542,6 +545,487 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   }
 }
 
+// ---- the pair kernel: two CTAs of a cluster on one K/V stream ---------------------------------------
+// A cluster of two CTAs (cta_group::2) owns (request, kv head, two q tiles of 128/G tokens), one q
+// tile per CTA. One MMA covers both tiles (M = 256: rows 0-127 in CTA 0's TMEM, 128-255 in CTA 1's),
+// so a K/V block feeds two q tiles while each CTA loads and holds only half of it: for S = Q K^T
+// (N = 128 kv tokens) CTA c holds tokens [64c, 64c+64) of the block, for O += P V (N = head_dim) it
+// holds the 64-element half c of head_dim. Per SM that is the K/V traffic of prefill_kernel (one
+// block per two q tiles) with half the B-operand reads from shared memory.
+//
+// With one q tile per CTA the 512 TMEM columns hold S twice (S0 at 0, S1 at 128), O (at 256) and
+// P twice (P0 at 384, P1 at 448). The two softmax warp groups take alternate K/V blocks: group a
+// works on the blocks j = a (mod 2). It gives S_a back as soon as the row is in registers, so Q K^T
+// of block j+2 runs while the group is still busy with block j and S is there when it comes back;
+// P_j goes to P_a, which P V of block j reads while the group already works on block j+2. Neither
+// group waits for the tensor core in steady state, and the special-function unit sees the two
+// groups half a block apart. What the groups share per row is the reference maximum of the lazily rescaled
+// softmax: the group of block j reads the reference left by block j-1 (shared memory, a named
+// barrier per warp pair), raises it if its own row maximum is more than 2^8 above it, and publishes
+// it; only the group that raises it rescales O (after P V of block j-1 has finished), and each group
+// brings its own partial row sum to the current reference when it next sees it.
+//
+// Two threads of CTA 0 issue the MMAs: warp 9 the Q K^T products, warp 11 the P V products.
+// Barriers those threads wait on (q, kfull, vfull, sfree, pfull) live in CTA 0 and are signalled by
+// both CTAs (TMA complete_tx through the cta_group::2 form, remote arrives); barriers the other
+// warps wait on (kempty, vempty, sfull, pvdone) exist in both CTAs and are committed to in both.
+// Every wait is bounded; both CTAs meet at a cluster barrier before the TMEM is freed.
+constexpr int kPairThreads = 384;  // 2 x 4 softmax warps, q + K producer, Q K^T issuer, V producer, P V issuer
+constexpr int kPStages = 4;        // K blocks and V blocks in flight, each
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {  // shared::cta -> shared::cluster of `rank`
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Arrivals on a barrier of any CTA of the cluster (address from map_to_cta). The plain form orders
+// nothing but the tensor-memory traffic that tcgen05.wait and tcgen05.fence have already closed; the
+// release form (hundreds of cycles) is for shared-memory writes the waiting side reads.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// TMA loads of a CTA pair: the data lands in this CTA, the bytes are counted on `bar`, which may be
+// the peer's barrier
+__device__ __forceinline__ void tma2_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                             int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::
+          "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::
+          "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// completion of the MMAs issued so far by this thread: one arrival on the barrier at this offset in
+// each of the two CTAs
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar_cluster) {
+  asm volatile(
+      "{\n .reg .b16 m;\n mov.b16 m, 3;\n"
+      " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n}\n" ::"r"(
+          bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_ss_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile("tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, 1;\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+               "r"(idesc)
+               : "memory");
+}
+__device__ __forceinline__ void umma2_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  asm volatile("tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, 1;\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc),
+               "r"(idesc)
+               : "memory");
+}
+__device__ __forceinline__ void named_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Warp roles: 0-3 softmax of the even K/V blocks, 4-7 of the odd ones (thread = row = TMEM lane),
+// 8 TMA producer of q and the K ring, 9 Q K^T issuer (CTA 0), 10 TMA producer of the V ring,
+// 11 P V issuer (CTA 0).
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                    const PrefillParams p) {
+  constexpr int D = 128, DH = 2;
+  constexpr int QTILE = 128 * D * 2;        // the q tile: [DH][128 rows][128 B]
+  constexpr int KHALF = 64 * 128;           // this CTA's 64 tokens of a K block, one 64-element half of head_dim
+  constexpr int KSTAGE = DH * KHALF;        // [DH][64 tokens][128 B]
+  constexpr int VSTAGE = kBN * 128;         // [128 tokens][128 B]: this CTA's 64-element half of head_dim
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
+  constexpr uint32_t IDESC_QK = instr_desc(kBf16 ? 1 : 0, 0, kBN, 256);
+  constexpr uint32_t IDESC_PV = instr_desc(kBf16 ? 1 : 0, 1, D, 256);
+  constexpr uint32_t COL_O = 256, COL_P = 384;  // S0 at 0, S1 at 128; P0 at 384, P1 at 448
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = q_smem + QTILE;                  // kPStages stages
+  const uint32_t v_smem = k_smem + kPStages * KSTAGE;      // kPStages stages
+  const uint32_t f_smem = v_smem + kPStages * VSTAGE;      // floats: mref[2][128], lsum[2][128], mfin[2][128]
+  const uint32_t bars = f_smem + 6 * 128 * 4;
+  float* fl = reinterpret_cast<float*>(smem + (f_smem - base));
+  float* mref = fl;             // [group][row]: the reference maximum after that group's latest block
+  float* lsum = fl + 256;       // [group][row]: partial row sums, for the epilogue
+  float* mfin = fl + 512;       // [group][row]: the reference each partial sum is scaled to
+  // barrier slots (8 bytes each)
+  constexpr uint32_t B_Q = 0, B_KFULL = 1, B_VFULL = B_KFULL + kPStages, B_KEMPTY = B_VFULL + kPStages,
+                     B_VEMPTY = B_KEMPTY + kPStages, B_SFULL = B_VEMPTY + kPStages, B_PFULL = B_SFULL + 2,
+                     B_PVDONE = B_PFULL + 2, B_SFREE = B_PVDONE + 2, B_VLAST = B_SFREE + 2, B_MREF = B_VLAST + 1,
+                     B_COUNT = B_MREF + 8;  // mref: [group][warp of the group], one arrival per published block
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 8 * B_COUNT);
+  auto bar = [&](uint32_t slot) { return bars + 8 * slot; };
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster_ctarank();
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int tq = 128 / G;                  // q tokens per tile
+  const int kv_head = blockIdx.y;
+  const int ps_log = p.ps_log2, ps = 1 << ps_log;
+  const int bt = min(ps, 16);
+
+  const int4 item = p.items[blockIdx.x >> 1];
+  const int req = item.x, q0 = item.y, nq = item.z, kv_hi = item.w;
+  const int q_begin = __ldg(p.qo_indptr + req);
+  const int n_new = __ldg(p.qo_indptr + req + 1) - q_begin;
+  const int ip0 = __ldg(p.kv_indptr + req), ip1 = __ldg(p.kv_indptr + req + 1);
+  const int kv_len = ip1 > ip0 ? (ip1 - ip0 - 1) * ps + __ldg(p.kv_last_page_len + req) : 0;
+  const int n_blocks = (kv_hi + kBN - 1) / kBN;
+  // the same verdict in both CTAs of the pair: both leave before any cluster-wide step
+  const bool bad = q0 < 0 || nq < 1 || nq > 2 * tq || q0 + nq > n_new || kv_hi < 1 || kv_hi > kv_len;
+  if (bad) {
+    if (tid == 0) record_status(p.status, ST_BAD_PLAN);
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(bar(B_Q), 2);  // one arrival (with its byte count) per CTA
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(bar(B_KFULL + s), 2);
+      mbar_init(bar(B_VFULL + s), 2);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(B_SFULL + s), 1);
+      mbar_init(bar(B_PFULL + s), 8);  // one arrival per warp of the softmax group, both CTAs
+      mbar_init(bar(B_SFREE + s), 8);
+      mbar_init(bar(B_PVDONE + s), 1);
+    }
+    mbar_init(bar(B_VLAST), 1);
+    for (int s = 0; s < 8; ++s) mbar_init(bar(B_MREF + s), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 8) {  // TMEM: all 512 columns of both SMs; the same warp of both CTAs takes part
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lead = map_to_cta(bars, 0) - bars;  // add to a local barrier address: the same barrier in CTA 0
+
+  if (warp == 8) {
+    // ================================ q and the K ring ==========================================
+    if (lane == 0) {
+      mbar_expect_tx_cluster(bar(B_Q) + lead, (uint32_t)QTILE);
+      for (int dh = 0; dh < DH; ++dh)
+        tma2_load_4d(q_smem + dh * (128 * 128), &q_map, bar(B_Q) + lead, 0, kv_head * G, dh,
+                     q_begin + q0 + (int)rank * tq);
+    }
+    const int32_t* idx = p.kv_indices + ip0;
+    const int n_boxes = 64 / bt;
+    for (int j = 0; j < n_blocks; ++j) {
+      const int s = j % kPStages, round = j / kPStages;
+      const int t0 = j * kBN + (int)rank * 64;  // this CTA's 64 tokens of the block
+      int live = 0;
+      for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
+      if (round > 0 && !warp_wait(bar(B_KEMPTY + s), (round - 1) & 1, p.status)) break;
+      if (lane == 0) mbar_expect_tx_cluster(bar(B_KFULL + s) + lead, (uint32_t)(live * DH * bt * 128));
+      __syncwarp();
+      for (int b = lane; b < n_boxes; b += 32) {
+        const int tok = t0 + b * bt;
+        if (tok >= kv_hi) continue;
+        int page = __ldg(idx + (tok >> ps_log));
+        if (page < 0 || page >= p.num_pages) {
+          record_status(p.status, ST_BAD_PAGE_ID);
+          page = 0;
+        }
+        const int in_page = tok & (ps - 1);
+        for (int dh = 0; dh < DH; ++dh)
+          tma2_load_5d(k_smem + (uint32_t)(s * KSTAGE + dh * KHALF + b * bt * 128), &kv_map, bar(B_KFULL + s) + lead, 0,
+                       in_page, kv_head, dh, 2 * page);
+      }
+    }
+  } else if (warp == 10) {
+    // ================================ the V ring: this CTA's half of head_dim ====================
+    const int32_t* idx = p.kv_indices + ip0;
+    const int n_boxes = kBN / bt;
+    for (int j = 0; j < n_blocks; ++j) {
+      const int s = j % kPStages, round = j / kPStages;
+      const int t0 = j * kBN;
+      const int cols = min(kBN, kv_hi - t0);
+      // Rows past the visible length inside the last 16-token step hold whatever the pool left
+      // there; 0 * garbage must stay 0, so that block goes through a local barrier, the rows are
+      // cleared, and the arrival on CTA 0's barrier is a plain one.
+      const bool ragged = (cols & 15) != 0;
+      int live = 0;
+      for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
+      if (round > 0 && !warp_wait(bar(B_VEMPTY + s), (round - 1) & 1, p.status)) break;
+      const uint32_t full = ragged ? bar(B_VLAST) : bar(B_VFULL + s) + lead;
+      if (lane == 0) {
+        if (ragged) mbar_expect_tx(full, (uint32_t)(live * bt * 128));
+        else mbar_expect_tx_cluster(full, (uint32_t)(live * bt * 128));
+      }
+      __syncwarp();
+      for (int b = lane; b < n_boxes; b += 32) {
+        const int tok = t0 + b * bt;
+        if (tok >= kv_hi) continue;
+        int page = __ldg(idx + (tok >> ps_log));
+        if (page < 0 || page >= p.num_pages) {
+          record_status(p.status, ST_BAD_PAGE_ID);
+          page = 0;
+        }
+        const int in_page = tok & (ps - 1);
+        tma2_load_5d(v_smem + (uint32_t)(s * VSTAGE + b * bt * 128), &kv_map, full, 0, in_page, kv_head, (int)rank,
+                     2 * page + 1);
+      }
+      if (ragged) {  // only the last block of the item can be ragged: the local barrier is used once
+        if (!warp_wait(bar(B_VLAST), 0, p.status)) break;
+        const int r0 = cols, r1 = (cols + 15) & ~15;
+        for (int z = lane; z < (r1 - r0) * 8; z += 32)
+          *reinterpret_cast<uint4*>(smem + (v_smem - base) + s * VSTAGE + (r0 + (z >> 3)) * 128 + (z & 7) * 16) =
+              make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_release(bar(B_VFULL + s) + lead);
+      }
+    }
+  } else if (warp == 9) {
+    // ================================ Q K^T issuer: one thread of CTA 0 ==========================
+    if (rank == 0 && lane == 0) {
+      bool ok = mbar_wait(bar(B_Q), 0, p.status);
+      const uint64_t qd = smem_desc(q_smem, 16, 1024);
+      const uint64_t kd0 = smem_desc(k_smem, 16, 1024);
+      for (int j = 0; ok && j < n_blocks; ++j) {
+        const int s = j % kPStages, a = j & 1;
+        ok = mbar_wait(bar(B_KFULL + s), (j / kPStages) & 1, p.status);
+        // S_a is free once its group has block j-2 in registers
+        if (ok && j >= 2) ok = mbar_wait(bar(B_SFREE + a), ((j - 2) >> 1) & 1, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d = tmem + a * kBN;
+        const uint64_t kb = kd0 + (uint64_t)(s * (KSTAGE / 16));
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t qoff = (uint64_t)(((kk >> 2) * (128 * 128) + (kk & 3) * 32) / 16);
+          const uint64_t koff = (uint64_t)(((kk >> 2) * KHALF + (kk & 3) * 32) / 16);
+          if (kk == 0) umma2_ss(d, qd + qoff, kb + koff, IDESC_QK, 0u);
+          else umma2_ss_acc(d, qd + qoff, kb + koff, IDESC_QK);
+        }
+        tc2_commit_both(bar(B_SFULL + a));
+        tc2_commit_both(bar(B_KEMPTY + s));
+      }
+    }
+  } else if (warp == 11) {
+    // ================================ P V issuer: one thread of CTA 0 ============================
+    if (rank == 0 && lane == 0) {
+      const uint64_t vd0 = smem_desc(v_smem, VSTAGE, 1024);
+      bool ok = true;
+      for (int j = 0; ok && j < n_blocks; ++j) {
+        const int s = j % kPStages, a = j & 1;
+        ok = mbar_wait(bar(B_VFULL + s), (j / kPStages) & 1, p.status);
+        if (ok) ok = mbar_wait(bar(B_PFULL + a), (j >> 1) & 1, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const int cols = min(kBN, kv_hi - j * kBN);
+        const int ksteps = (cols + 15) >> 4;  // 16-token steps that hold a visible token
+        const uint32_t d = tmem + COL_O, pa = tmem + COL_P + a * (kBN / 2);
+        const uint64_t vb = vd0 + (uint64_t)(s * (VSTAGE / 16));
+        if (ksteps == kBN / 16 && j > 0) {  // the common case, fully unrolled
+#pragma unroll
+          for (int kt = 0; kt < kBN / 16; ++kt) umma2_ts_acc(d, pa + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV);
+        } else {
+          for (int kt = 0; kt < ksteps; ++kt)
+            umma2_ts(d, pa + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV, (j > 0 || kt > 0) ? 1u : 0u);
+        }
+        tc2_commit_both(bar(B_PVDONE + a));  // P_a is free, O holds block j
+        tc2_commit_both(bar(B_VEMPTY + s));
+      }
+    }
+  } else {
+    // ================================ softmax / correction / epilogue ============================
+    const int a = warp >> 2;                  // this group's blocks: j = a (mod 2), in S_a
+    const int row = tid & 127;                // TMEM lane and MMA row
+    const int tok_local = (int)rank * tq + row / G, head = row % G;
+    const bool row_live = tok_local < nq;
+    const int limit = min(p.causal ? (kv_len - n_new + q0 + tok_local) : (kv_len - 1), kv_hi - 1);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + a * kBN;
+    const uint32_t p_addr = tmem + lane_base + COL_P + a * (kBN / 2);
+    const uint32_t o_addr = tmem + lane_base + COL_O;
+    // the warp of the other group that owns the same rows publishes its reference on its barrier
+    const uint32_t bar_mine = bar(B_MREF + 4 * a + (warp & 3)), bar_other = bar(B_MREF + 4 * (1 - a) + (warp & 3));
+    const float sc = p.scale_log2;
+    float m_mine = -INFINITY, l = 0.f;        // l is scaled to the reference m_mine
+    bool ok = true;
+    for (int j = a; j < n_blocks; j += 2) {
+      if (!warp_wait(bar(B_SFULL + a), (j >> 1) & 1, p.status)) { ok = false; break; }
+      tc_fence_after();
+      const int t0 = j * kBN;
+      uint32_t r[kBN];
+#pragma unroll
+      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(bar(B_SFREE + a) + lead);  // S_a may take Q K^T of block j+2
+      if (t0 + kBN - 1 > limit) {
+#pragma unroll
+        for (int i = 0; i < kBN; ++i)
+          if (t0 + i > limit) r[i] = 0xff800000u;  // -inf
+      }
+      float mx;
+      {
+        float m8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m8[i] = __uint_as_float(r[i]);
+#pragma unroll
+        for (int i = 8; i + 15 < kBN; i += 16) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            m8[q] = fmax3(m8[q], __uint_as_float(r[i + 2 * q]), __uint_as_float(r[i + 2 * q + 1]));
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) m8[q] = fmaxf(m8[q], __uint_as_float(r[kBN - 8 + q]));  // 8 + 7 * 16 = 120 done
+        mx = fmaxf(fmax3(m8[0], m8[1], m8[2]), fmaxf(fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+      }
+      const float m_tile = mx * sc;
+      // the reference maximum block j-1 left (the other group's latest), then ours
+      float m_prev = -INFINITY;
+      if (j > 0) {  // block j-1 is the other group's ((j-1)/2)-th
+        if (!warp_wait(bar_other, ((j - 1) >> 1) & 1, p.status)) { ok = false; break; }
+        m_prev = mref[(1 - a) * 128 + row];
+      }
+      float m_new = m_prev;
+      if (m_tile > m_prev + kRescaleThreshold || (m_prev == -INFINITY && m_tile > -INFINITY)) m_new = m_tile;
+      if (j + 1 < n_blocks) {
+        mref[a * 128 + row] = m_new;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_mine);
+      }
+      if (m_new != m_mine) {  // bring this group's partial sum to the current reference
+        l *= (m_mine == -INFINITY) ? 0.f : exp2f(m_mine - m_new);
+        m_mine = m_new;
+      }
+      // P_a is free once P V of block j-2 has read it (long ago, as a rule). Products finish in
+      // order, so the other group's barrier is then past block j-3 and a wait for block j-1 on it
+      // cannot be answered by an older phase.
+      if (j >= 2 && !warp_wait(bar(B_PVDONE + a), ((j - 2) >> 1) & 1, p.status)) { ok = false; break; }
+      if (j > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
+        // O takes in block j-1 until that product has finished
+        if (!warp_wait(bar(B_PVDONE + (1 - a)), ((j - 1) >> 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const float factor = (m_prev == -INFINITY) ? 0.f : exp2f(m_prev - m_new);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st32(o_addr + c * 32, o);
+        }
+      }
+      const float off = (m_new == -INFINITY) ? 0.f : m_new;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float x0, x1, e0, e1;
+          ffma2(x0, x1, __uint_as_float(r[c * 32 + 2 * i]), __uint_as_float(r[c * 32 + 2 * i + 1]), sc, sc, -off, -off);
+          e0 = ex2(x0);
+          e1 = ex2(x1);
+          fadd2(ls[2 * (i & 1)], ls[2 * (i & 1) + 1], ls[2 * (i & 1)], ls[2 * (i & 1) + 1], e0, e1);
+          pk[i] = pack2<T>(e0, e1);
+        }
+        tmem_st16(p_addr + c * 16, pk);
+      }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(bar(B_PFULL + a) + lead);
+    }
+    // ---- epilogue: both groups' partial sums at the final reference, each stores half of head_dim
+    lsum[a * 128 + row] = l;
+    mfin[a * 128 + row] = m_mine;
+    named_sync(9, 256);
+    // the last product: first this group's own last one (its barrier is at most one phase behind),
+    // after which the other group's barrier is in the phase of the very last block
+    const int j_last = n_blocks - 1 - ((n_blocks - 1 - a) & 1);
+    if (ok && j_last >= 0) ok = warp_wait(bar(B_PVDONE + a), (j_last >> 1) & 1, p.status);
+    if (ok) ok = warp_wait(bar(B_PVDONE + ((n_blocks - 1) & 1)), ((n_blocks - 1) >> 1) & 1, p.status);
+    if (ok) {
+      tc_fence_after();
+      // O is scaled to the reference of the group that worked on the last block
+      const int last = (n_blocks - 1) & 1;
+      const float m_fin = mfin[last * 128 + row], m_oth = mfin[(1 - last) * 128 + row];
+      const float l_oth = lsum[(1 - last) * 128 + row];
+      const float l_all = lsum[last * 128 + row] + ((m_oth == -INFINITY) ? 0.f : l_oth * exp2f(m_oth - m_fin));
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      T* dst = reinterpret_cast<T*>(p.out) + (int64_t)(q_begin + q0 + tok_local) * p.out_stride +
+               (int64_t)(kv_head * G + head) * D + a * 64;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + a * 64 + c * 32, o);
+        tmem_wait_ld();
+        if (row_live) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack2<T>(__uint_as_float(o[v * 8 + 2 * i]) * inv, __uint_as_float(o[v * 8 + 2 * i + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: both CTAs meet (the peer's shared memory and TMEM are in use until here) -------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 8) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
 // ---- host -------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -582,24 +1066,36 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
   DSV_REQUIRE(G <= 128 && 128 % G == 0, "prefill_plan: GQA group %d must divide 128", G);
   const int tq = 128 / G;
   struct Item { int req, q0, nq, hi; };
-  std::vector<Item> items;
+  // A pair item is two q tiles of one request for a cluster of two CTAs (one tile each); a request's
+  // last tile, when it is alone, is a single-CTA item. The pair kernel exists for head_dim 128;
+  // without it an item is two q tiles for one CTA.
+  std::vector<Item> items, pairs;
+  // (the pair kernel is still the slower one on the benchmark shape: opt-in until it is not)
+  const char* pairs_env = std::getenv("DESERVE_PREFILL_PAIRS");
+  const bool use_pairs = head_dim == 128 && pairs_env != nullptr && pairs_env[0] == '1';
   for (int i = 0; i < batch; ++i) {
     const int n = qo_indptr_host[i + 1] - qo_indptr_host[i];
     const int len = kv_len_host[i];
     DSV_REQUIRE(n >= 0 && len >= n, "prefill_plan: request %d has %d new tokens but kv length %d", i, n, len);
     if (n < min_new_tokens) continue;  // left to another kernel (decode rows of a mixed batch)
-    for (int q0 = 0; q0 < n; q0 += 2 * tq) {  // a work item is two q tiles of the same request
-      const int nq = std::min(2 * tq, n - q0);
-      const int hi = causal ? len - n + q0 + nq : len;  // kv positions the tile's last token sees
-      items.push_back({i, q0, nq, hi});
+    int q0 = 0;
+    while (q0 < n) {
+      const int left = n - q0;
+      const bool pair = use_pairs && left > tq;
+      const int nq = std::min(2 * tq, left);
+      const int hi = causal ? len - n + q0 + nq : len;  // kv positions the item's last token sees
+      (pair ? pairs : items).push_back({i, q0, nq, hi});
+      q0 += nq;
     }
   }
-  const int64_t need = kPlanHeader + 4 * (int64_t)items.size();
+  const int64_t need = kPlanHeader + 4 * (int64_t)(items.size() + pairs.size());
   *plan_used_i32 = need;
   if (need > plan_capacity_i32)
     return fail(DSV_E_WORKSPACE, "prefill_plan: plan needs %lld int32, capacity %lld", (long long)need,
                 (long long)plan_capacity_i32);
-  std::stable_sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.hi > b.hi; });
+  auto longest_first = [](const Item& a, const Item& b) { return a.hi > b.hi; };
+  std::stable_sort(items.begin(), items.end(), longest_first);
+  std::stable_sort(pairs.begin(), pairs.end(), longest_first);
   plan_host[0] = kPrefillMagic;
   plan_host[1] = (int32_t)items.size();
   plan_host[2] = tq;
@@ -608,11 +1104,15 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
   plan_host[5] = kPlanHeader;
   plan_host[6] = n_q_heads;
   plan_host[7] = n_kv_heads;
-  for (size_t k = 0; k < items.size(); ++k) {
+  plan_host[8] = (int32_t)pairs.size();
+  plan_host[9] = kPlanHeader + 4 * (int32_t)items.size();
+  plan_host[10] = plan_host[11] = 0;
+  for (size_t k = 0; k < items.size() + pairs.size(); ++k) {
+    const Item& src = k < items.size() ? items[k] : pairs[k - items.size()];
     int32_t* it = plan_host + kPlanHeader + 4 * k;
-    it[0] = items[k].req; it[1] = items[k].q0; it[2] = items[k].nq; it[3] = items[k].hi;
+    it[0] = src.req; it[1] = src.q0; it[2] = src.nq; it[3] = src.hi;
   }
-  (void)head_dim; (void)page_size; (void)dtype;
+  (void)page_size; (void)dtype;
   return DSV_OK;
 }
 
@@ -645,8 +1145,9 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
               "prefill: pointers and strides must be 16-byte aligned");
   DSV_REQUIRE(q_stride_tok >= (int64_t)n_q_heads * head_dim && out_stride_tok >= (int64_t)n_q_heads * head_dim,
               "prefill: token stride smaller than a row");
-  const int n_items = plan_host[1];
-  if (n_items == 0) return DSV_OK;
+  const int n_items = plan_host[1], n_pairs = plan_host[8];
+  DSV_REQUIRE(n_items >= 0 && n_pairs >= 0 && (n_pairs == 0 || head_dim == 128), "prefill: corrupt plan");
+  if (n_items == 0 && n_pairs == 0) return DSV_OK;
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return fail(DSV_E_CUDA, "prefill: cuTensorMapEncodeTiled is not available");
   const CUtensorMapDataType dt = dtype == DSV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -678,19 +1179,30 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
   p.out_stride = out_stride_tok; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.ps_log2 = ps_log2;
   p.num_pages = (int)num_pages; p.causal = causal ? 1 : 0; p.scale_log2 = sm_scale * kLog2e;
   p.status = device_status_ptr();
-  const size_t smem = (size_t)2 * 128 * head_dim * 2 + (size_t)(2 + kVStages) * kBN * head_dim * 2 + 256 + 1024;
-  const dim3 grid((unsigned)n_items, (unsigned)n_kv_heads);
-  auto go = [&](auto kernel) -> cudaError_t {
+  auto go = [&](auto kernel, dim3 grid, int threads, size_t smem, const PrefillParams& pp) -> cudaError_t {
     cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (er != cudaSuccess) return er;
-    kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(q_map, kv_map, p);
+    kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(q_map, kv_map, pp);
     return cudaGetLastError();
   };
-  cudaError_t e;
-  if (dtype == DSV_BF16)
-    e = head_dim == 128 ? go(prefill_kernel<__nv_bfloat16, 128>) : go(prefill_kernel<__nv_bfloat16, 64>);
-  else
-    e = head_dim == 128 ? go(prefill_kernel<__half, 128>) : go(prefill_kernel<__half, 64>);
+  cudaError_t e = cudaSuccess;
+  if (n_pairs > 0) {  // the long items first: a cluster of two CTAs per item and kv head
+    PrefillParams pp = p;
+    pp.items = reinterpret_cast<const int4*>(plan_dev + plan_host[9]);
+    const size_t smem = (size_t)128 * 128 * 2 + (size_t)kPStages * (2 * 64 * 128 + kBN * 128) + 6 * 128 * 4 + 512 + 1024;
+    const dim3 grid(2u * (unsigned)n_pairs, (unsigned)n_kv_heads);
+    e = dtype == DSV_BF16 ? go(prefill_pair_kernel<__nv_bfloat16>, grid, kPairThreads, smem, pp)
+                          : go(prefill_pair_kernel<__half>, grid, kPairThreads, smem, pp);
+  }
+  if (e == cudaSuccess && n_items > 0) {
+    const size_t smem = (size_t)2 * 128 * head_dim * 2 + (size_t)(2 + kVStages) * kBN * head_dim * 2 + 256 + 1024;
+    const dim3 grid((unsigned)n_items, (unsigned)n_kv_heads);
+    if (dtype == DSV_BF16)
+      e = head_dim == 128 ? go(prefill_kernel<__nv_bfloat16, 128>, grid, kThreads, smem, p)
+                          : go(prefill_kernel<__nv_bfloat16, 64>, grid, kThreads, smem, p);
+    else
+      e = head_dim == 128 ? go(prefill_kernel<__half, 128>, grid, kThreads, smem, p) : go(prefill_kernel<__half, 64>, grid, kThreads, smem, p);
+  }
   if (e != cudaSuccess) return fail(DSV_E_CUDA, "prefill launch failed: %s", cudaGetErrorString(e));
   return DSV_OK;
 }

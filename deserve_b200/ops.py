@@ -212,9 +212,12 @@ class BatchDecodeWithPagedKVCacheWrapper:
         self._desc = None
 
 
+_PREFILL_PLAN_HEADER = 12
+
+
 def prefill_plan_capacity(nnz: int, batch: int, group: int) -> int:
     tq = max(1, 128 // group)
-    return _PLAN_HEADER + 4 * (nnz // tq + batch + 1)
+    return _PREFILL_PLAN_HEADER + 4 * (nnz // tq + batch + 1)
 
 
 def make_prefill_plan(qo_indptr_host: np.ndarray, kv_len_host: np.ndarray, n_q_heads: int, n_kv_heads: int,
@@ -252,7 +255,8 @@ def paged_prefill(q: torch.Tensor, qo_indptr: torch.Tensor, paged_kv_cache: torc
         kv_indices.data_ptr(), kv_indptr.data_ptr(), kv_last_page_len.data_ptr(), out.data_ptr(), os_,
         plan_host.ctypes.data, plan_dev.data_ptr(), kv_last_page_len.shape[0], nnz, hq, hkv, d, ps,
         _lib.dtype_code(q.dtype), float(sm_scale), 1 if causal else 0, _lib.current_stream_ptr(q.device)))
-    _lib.LAUNCHES[0] += 1
+    # one launch for the pair items (clusters of two CTAs), one for the single-CTA items
+    _lib.LAUNCHES[0] += int(plan_host[1] > 0) + int(plan_host[8] > 0)
     return out
 
 
@@ -372,7 +376,7 @@ class BatchPrefillWithPagedKVCacheWrapper:
         head = self._ws[: self._PLAN_BYTES].view(torch.int32)
         if out is None:
             out = torch.empty((q.shape[0], hq, d), dtype=q.dtype, device=q.device)
-        if self._plan_host[1] > 0:
+        if self._plan_host[1] > 0 or self._plan_host[8] > 0:  # single-CTA items, pair items
             paged_prefill(q, qo, paged_kv_cache, kv_indices, kv_indptr, last, self._plan_host, head, out, sm_scale, causal)
         if self._dec is not None:
             o_plan, d_used, o_ip, o_last, o_rows, o_idx, n_dec, n_idx, plan_host = self._dec

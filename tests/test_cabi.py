@@ -122,22 +122,35 @@ def test_decode_plan_rejects_bad_input():
 
 
 @pytest.mark.parametrize("causal", [True, False])
-def test_prefill_plan_tiles_every_new_token_once(causal):
+def test_prefill_plan_tiles_every_new_token_once(causal, monkeypatch):
+    monkeypatch.setenv("DESERVE_PREFILL_PAIRS", "1")
     qo = np.array([0, 100, 101, 613, 613, 650], dtype=np.int32)
     kv_len = np.array([100, 900, 1024, 7, 37], dtype=np.int32)
     plan = np.zeros(ops.prefill_plan_capacity(650, 5, 4), dtype=np.int32)
     used = ops.make_prefill_plan(qo, kv_len, 32, 8, 128, 16, torch.bfloat16, causal, plan)
-    n_items, tq = plan[1], plan[2]
-    assert tq == 32 and used == 8 + 4 * n_items and plan[3] == int(causal)
-    items = plan[8:used].reshape(-1, 4)
+    n_items, tq, n_pairs = plan[1], plan[2], plan[8]
+    assert tq == 32 and used == 12 + 4 * (n_items + n_pairs) and plan[3] == int(causal)
+    assert plan[5] == 12 and plan[9] == 12 + 4 * n_items
+    singles = plan[12 : 12 + 4 * n_items].reshape(-1, 4)
+    pairs = plan[plan[9] : used].reshape(-1, 4)
     cover = [np.zeros(n, dtype=int) for n in np.diff(qo)]
-    for req, q0, nq, hi in items:
-        assert 1 <= nq <= 2 * tq and q0 % (2 * tq) == 0  # an item is two q tiles
-        cover[req][q0 : q0 + nq] += 1
-        n = qo[req + 1] - qo[req]
-        assert hi == (kv_len[req] - n + q0 + nq if causal else kv_len[req])
+    # head_dim 128: a pair item is two q tiles (one per CTA of a cluster), a single-CTA item a lone last tile
+    for lo, hi_, items in ((0, tq, singles), (tq, 2 * tq, pairs)):
+        for req, q0, nq, hi in items:
+            assert lo < nq <= hi_ and q0 % (2 * tq) == 0
+            cover[req][q0 : q0 + nq] += 1
+            n = qo[req + 1] - qo[req]
+            assert hi == (kv_len[req] - n + q0 + nq if causal else kv_len[req])
+        assert (np.diff(items[:, 3]) <= 0).all()  # most work first
     assert all((c == 1).all() for c in cover)
-    assert (np.diff(items[:, 3]) <= 0).all()  # most work first
+    assert n_pairs == 11 and n_items == 1  # 100 -> 64 + 36; 1 -> a single; 512 -> 8 x 64; 37 -> one pair
+
+
+def test_prefill_plan_head_dim_64_has_no_pair_items():
+    qo = np.array([0, 300], dtype=np.int32)
+    plan = np.zeros(ops.prefill_plan_capacity(300, 1, 4), dtype=np.int32)
+    ops.make_prefill_plan(qo, np.array([300], dtype=np.int32), 8, 2, 64, 16, torch.float16, True, plan)
+    assert plan[8] == 0 and plan[1] == 5  # 300 tokens in items of 64
 
 
 def test_prefill_plan_rejects_inconsistent_lengths():

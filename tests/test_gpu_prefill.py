@@ -14,8 +14,11 @@ pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 
 
-@pytest.fixture(autouse=True)
-def _device_status_clean():
+@pytest.fixture(autouse=True, params=["single", "pairs"])
+def _device_status_clean(request, monkeypatch):
+    # every case runs twice: single-CTA items only, and with the two-CTA pair kernel taking the items of
+    # more than one q tile (head_dim 128)
+    monkeypatch.setenv("DESERVE_PREFILL_PAIRS", "1" if request.param == "pairs" else "0")
     yield
     assert _lib.read_device_status() == 0, "a kernel self-check fired"
 
@@ -95,6 +98,26 @@ def test_small_workspace_keeps_decode_rows_in_the_prefill_kernel():
 def test_tile_and_page_boundaries():
     lens = [127, 128, 129, 255, 256, 257, 15, 16, 17, 1]
     err, _ = _run(4, lens, lens, 8, 2, 64, 16, torch.float16, poison=True)
+    assert err <= 2e-2, f"max-abs error {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_pair_items_around_block_and_tile_boundaries(dtype):
+    # head_dim 128, GQA 4: every 64 new tokens (two q tiles) are worked by a cluster of two CTAs, the
+    # two softmax groups of a CTA taking alternate 128-token K/V blocks. Lengths around the tile and
+    # block sizes, one to many blocks, ragged last blocks (not a multiple of 16: the poisoned tail of
+    # the last page must not leak), items whose second tile is partly or wholly empty, a context of 0.
+    new = [65, 96, 97, 128, 129, 191, 192, 193, 70, 300]
+    ctx = [0, 31, 0, 64, 1000, 63, 7, 515, 2041, 1]
+    lens = [c + n for c, n in zip(ctx, new)]
+    err, _ = _run(11, lens, new, 32, 8, 128, 16, dtype, poison=True)
+    assert err <= 2e-2, f"max-abs error {err}"
+
+
+def test_pair_items_non_causal_and_wide_group():
+    err, _ = _run(12, [700, 333, 129], [130, 333, 129], 64, 8, 128, 16, torch.bfloat16, causal=False, poison=True)
+    assert err <= 2e-2, f"max-abs error {err}"
+    err, _ = _run(13, [1100, 600], [1030, 270], 4, 4, 128, 32, torch.bfloat16, poison=True)  # no grouping: 128-token tiles
     assert err <= 2e-2, f"max-abs error {err}"
 
 
