@@ -227,14 +227,28 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
 // producer of q and the K ring, 9 MMA issuer, 10 TMA producer of the V ring.
 // TMEM columns: tile X owns [256 X, 256 X + 256): S at +0 (P is written over its first 64 columns
 // once the row has been read), O at +128.
-template <typename T, int D>
+// MERGED (head_dim 128, pages of 16 tokens or more): a K/V box is 16 tokens x both 64-element halves of
+// head_dim, 4 KB instead of two boxes of 2 KB. The K/V feed is bound by the number of TMA boxes an SM can
+// issue (80-100 cycles each at 2 KB, 110-135 at 4 KB, whatever their rank), not by their bytes. K boxes
+// come through k_map, which splits the token index so that a box lands as [8-token group][half][8 tokens]
+// [128 B]: 8-token groups 2 KB apart for either half, which one K-major descriptor walks. V boxes come
+// through v_map as [half][16 tokens][128 B]; a 16-token step of P V is one box, halves 2 KB apart.
+template <typename T, int D, bool MERGED>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+               const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                const PrefillParams p) {
   constexpr int DH = D / 64;
   constexpr int QTILE = 128 * D * 2;      // one q tile: [DH][128 rows][128 B]
   constexpr int KVTILE = kBN * D * 2;     // one K (or V) stage: [DH][128 tokens][128 B]
   constexpr int HALF_ROWS = 128 * 128;    // bytes of one 64-element half: 128 rows x 128 B
+  static_assert(!MERGED || D == 128, "merged boxes hold both halves of a 128-element head");
+  // K stage: [DH][128 tokens][128 B], or merged [16 groups][DH][8 tokens][128 B]
+  constexpr int K_GROUP = MERGED ? 2048 : 1024;     // bytes between 8-token groups of one half
+  constexpr int K_HALF = MERGED ? 1024 : HALF_ROWS; // bytes between the halves of head_dim
+  // V stage: [DH][128 tokens][128 B], or merged [8 boxes][DH][16 tokens][128 B]
+  constexpr int V_STEP = MERGED ? 4096 : 2048;      // bytes between 16-token steps
+  constexpr int V_HALF = MERGED ? 2048 : HALF_ROWS;
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   constexpr uint32_t IDESC_QK = instr_desc(kBf16 ? 1 : 0, 0, kBN, 128);
   constexpr uint32_t IDESC_PV = instr_desc(kBf16 ? 1 : 0, 1, D, 128);
@@ -255,11 +269,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.n_q_heads / p.n_kv_heads;
   const int tq = 128 / G;                  // q tokens per tile
-  const int kv_head = blockIdx.y;
+  // consecutive CTAs are the kv heads of one item: together they read whole token rows of the same pages
+  const int kv_head = blockIdx.x % p.n_kv_heads;
   const int ps_log = p.ps_log2, ps = 1 << ps_log;
   const int bt = min(ps, 16), n_boxes = kBN / bt;
 
-  const int4 item = p.items[blockIdx.x];
+  const int4 item = p.items[blockIdx.x / p.n_kv_heads];
   const int req = item.x, q0 = item.y, nq = item.z, kv_hi = item.w;
   const int q_begin = __ldg(p.qo_indptr + req);
   const int n_new = __ldg(p.qo_indptr + req + 1) - q_begin;
@@ -332,9 +347,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           page = 0;
         }
         const int in_page = tok & (ps - 1);
-        for (int dh = 0; dh < DH; ++dh) {
-          const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
-          tma_load_5d((kv ? v_smem : k_smem) + off, &kv_map, full, 0, in_page, kv_head, dh, 2 * page + kv);
+        if constexpr (MERGED) {  // bt = 16: one 4 KB box per 16 tokens
+          const uint32_t dst = (kv ? v_smem : k_smem) + (uint32_t)(s * KVTILE + b * 4096);
+          if (kv) tma_load_5d(dst, &v_map, full, 0, in_page, kv_head, 0, 2 * page + 1);
+          else tma_load_5d(dst, &k_map, full, 0, 0, 2 * kv_head, in_page >> 3, 2 * page);
+        } else {
+          for (int dh = 0; dh < DH; ++dh) {
+            const uint32_t off = (uint32_t)(s * KVTILE + dh * HALF_ROWS + b * bt * 128);
+            tma_load_5d((kv ? v_smem : k_smem) + off, &kv_map, full, 0, in_page, kv_head, dh, 2 * page + kv);
+          }
         }
       }
     }
@@ -348,8 +369,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       // compile-time offset (the start-address field counts 16-byte units). The issuing thread is a
       // single lane: every instruction it spends per MMA is on the critical path of the tensor core.
       const uint64_t qd[2] = {smem_desc(q_smem, 16, 1024), smem_desc(q_smem + QTILE, 16, 1024)};
-      const uint64_t kd[2] = {smem_desc(k_smem, 16, 1024), smem_desc(k_smem + KVTILE, 16, 1024)};
-      const uint64_t vd0 = smem_desc(v_smem, HALF_ROWS, 1024);
+      const uint64_t kd[2] = {smem_desc(k_smem, 16, K_GROUP), smem_desc(k_smem + KVTILE, 16, K_GROUP)};
+      const uint64_t vd0 = smem_desc(v_smem, V_HALF, 1024);
       auto issue_qk = [&](int tile, int x) {  // S_x = Q_x K_tile^T
         const int s = tile & 1;
         const uint32_t d = tmem + x * COL_TILE + COL_S;
@@ -357,9 +378,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           constexpr int kUnit = 16;  // bytes per descriptor address unit
-          const uint64_t koff = (uint64_t)(((kk >> 2) * HALF_ROWS + (kk & 3) * 32) / kUnit);
-          if (kk == 0) umma_ss(d, qa + koff, kb + koff, IDESC_QK, 0u);
-          else umma_ss_acc(d, qa + koff, kb + koff, IDESC_QK);
+          const uint64_t qoff = (uint64_t)(((kk >> 2) * HALF_ROWS + (kk & 3) * 32) / kUnit);
+          const uint64_t koff = (uint64_t)(((kk >> 2) * K_HALF + (kk & 3) * 32) / kUnit);
+          if (kk == 0) umma_ss(d, qa + qoff, kb + koff, IDESC_QK, 0u);
+          else umma_ss_acc(d, qa + qoff, kb + koff, IDESC_QK);
         }
         tc_commit(bar_sfull + 8 * x);
         if (x == (has_b ? 1 : 0)) tc_commit(bar_kempty + 8 * s);  // last reader of this K stage
@@ -372,10 +394,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         const uint64_t vb = vd0 + (uint64_t)(s * (KVTILE / 16));
         if (ksteps == kBN / 16 && tile > 0) {  // the common case, fully unrolled
 #pragma unroll
-          for (int kt = 0; kt < kBN / 16; ++kt) umma_ts_acc(d, a + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV);
+          for (int kt = 0; kt < kBN / 16; ++kt) umma_ts_acc(d, a + kt * 8, vb + (uint64_t)(kt * V_STEP / 16), IDESC_PV);
         } else {
           for (int kt = 0; kt < ksteps; ++kt)
-            umma_ts(d, a + kt * 8, vb + (uint64_t)(kt * 2048 / 16), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
+            umma_ts(d, a + kt * 8, vb + (uint64_t)(kt * V_STEP / 16), IDESC_PV, (tile > 0 || kt > 0) ? 1u : 0u);
         }
         tc_commit(bar_odone + 8 * x);
         if (x == (has_b ? 1 : 0)) tc_commit(bar_vempty + 8 * s);  // last reader of this V stage
@@ -501,8 +523,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           const int r0 = cols, r1 = (cols + 15) & ~15;
           for (int z = row; z < (r1 - r0) * DH * 8; z += 128) {
             const int ch = z & 7, dh = (z >> 3) % DH, rr = r0 + (z >> 3) / DH;
-            *reinterpret_cast<uint4*>(smem + (v_smem - base) + vs * KVTILE + dh * HALF_ROWS + rr * 128 + ch * 16) =
-                make_uint4(0, 0, 0, 0);
+            const int at = MERGED ? (rr >> 4) * V_STEP + dh * V_HALF + (rr & 15) * 128 : dh * HALF_ROWS + rr * 128;
+            *reinterpret_cast<uint4*>(smem + (v_smem - base) + vs * KVTILE + at + ch * 16) = make_uint4(0, 0, 0, 0);
           }
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         }
@@ -571,7 +593,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 // warps wait on (kempty, vempty, sfull, pvdone) exist in both CTAs and are committed to in both.
 // Every wait is bounded; both CTAs meet at a cluster barrier before the TMEM is freed.
 constexpr int kPairThreads = 384;  // 2 x 4 softmax warps, q + K producer, Q K^T issuer, V producer, P V issuer
-constexpr int kPStages = 4;        // K blocks and V blocks in flight, each
+constexpr int kPKStages = 6;       // K blocks in flight (a load takes several block times to arrive)
+constexpr int kPVStages = 5;       // V blocks in flight
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -649,6 +672,20 @@ __device__ __forceinline__ void umma2_ts_acc(uint32_t d_tmem, uint32_t a_tmem, u
                "r"(idesc)
                : "memory");
 }
+// two barriers in one polling loop (a satisfied wait costs a few hundred cycles: pay it once)
+__device__ __forceinline__ bool warp_wait2(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b,
+                                           int* status) {
+  bool done = false;
+  for (int i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar_a, parity_a) && mbar_try_wait(bar_b, parity_b)) {
+      done = true;
+      break;
+    }
+    if (i > (1 << 16)) __nanosleep(64);
+  }
+  if (!done) record_status(status, ST_WAIT_TIMEOUT);
+  return __all_sync(0xffffffffu, done);
+}
 __device__ __forceinline__ void named_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }
@@ -659,11 +696,13 @@ __device__ __forceinline__ void named_sync(int id, int threads) {
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
-                    const PrefillParams p) {
+                    const __grid_constant__ CUtensorMap k_map, const PrefillParams p) {
   constexpr int D = 128, DH = 2;
   constexpr int QTILE = 128 * D * 2;        // the q tile: [DH][128 rows][128 B]
-  constexpr int KHALF = 64 * 128;           // this CTA's 64 tokens of a K block, one 64-element half of head_dim
-  constexpr int KSTAGE = DH * KHALF;        // [DH][64 tokens][128 B]
+  // this CTA's 64 tokens of a K block: [8-token group][half of head_dim][8 tokens][128 B]. One TMA box
+  // is 16 tokens x both halves (4 KB; the issue rate of TMA boxes, not their bytes, bounds the K/V feed).
+  constexpr int KGROUP = DH * 8 * 128;      // 2 KB
+  constexpr int KSTAGE = 8 * KGROUP;
   constexpr int VSTAGE = kBN * 128;         // [128 tokens][128 B]: this CTA's 64-element half of head_dim
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
   constexpr uint32_t IDESC_QK = instr_desc(kBf16 ? 1 : 0, 0, kBN, 256);
@@ -674,17 +713,17 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base;
-  const uint32_t k_smem = q_smem + QTILE;                  // kPStages stages
-  const uint32_t v_smem = k_smem + kPStages * KSTAGE;      // kPStages stages
-  const uint32_t f_smem = v_smem + kPStages * VSTAGE;      // floats: mref[2][128], lsum[2][128], mfin[2][128]
+  const uint32_t k_smem = q_smem + QTILE;
+  const uint32_t v_smem = k_smem + kPKStages * KSTAGE;
+  const uint32_t f_smem = v_smem + kPVStages * VSTAGE;     // floats: mref[2][128], lsum[2][128], mfin[2][128]
   const uint32_t bars = f_smem + 6 * 128 * 4;
   float* fl = reinterpret_cast<float*>(smem + (f_smem - base));
   float* mref = fl;             // [group][row]: the reference maximum after that group's latest block
   float* lsum = fl + 256;       // [group][row]: partial row sums, for the epilogue
   float* mfin = fl + 512;       // [group][row]: the reference each partial sum is scaled to
   // barrier slots (8 bytes each)
-  constexpr uint32_t B_Q = 0, B_KFULL = 1, B_VFULL = B_KFULL + kPStages, B_KEMPTY = B_VFULL + kPStages,
-                     B_VEMPTY = B_KEMPTY + kPStages, B_SFULL = B_VEMPTY + kPStages, B_PFULL = B_SFULL + 2,
+  constexpr uint32_t B_Q = 0, B_KFULL = 1, B_VFULL = B_KFULL + kPKStages, B_KEMPTY = B_VFULL + kPVStages,
+                     B_VEMPTY = B_KEMPTY + kPKStages, B_SFULL = B_VEMPTY + kPVStages, B_PFULL = B_SFULL + 2,
                      B_PVDONE = B_PFULL + 2, B_SFREE = B_PVDONE + 2, B_VLAST = B_SFREE + 2, B_MREF = B_VLAST + 1,
                      B_COUNT = B_MREF + 8;  // mref: [group][warp of the group], one arrival per published block
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + (bars - base) + 8 * B_COUNT);
@@ -694,11 +733,12 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   const uint32_t rank = cluster_ctarank();
   const int G = p.n_q_heads / p.n_kv_heads;
   const int tq = 128 / G;                  // q tokens per tile
-  const int kv_head = blockIdx.y;
+  // consecutive clusters are the kv heads of one item: together they read whole token rows of the same pages
+  const int kv_head = (blockIdx.x >> 1) % p.n_kv_heads;
   const int ps_log = p.ps_log2, ps = 1 << ps_log;
   const int bt = min(ps, 16);
 
-  const int4 item = p.items[blockIdx.x >> 1];
+  const int4 item = p.items[(blockIdx.x >> 1) / p.n_kv_heads];
   const int req = item.x, q0 = item.y, nq = item.z, kv_hi = item.w;
   const int q_begin = __ldg(p.qo_indptr + req);
   const int n_new = __ldg(p.qo_indptr + req + 1) - q_begin;
@@ -714,10 +754,12 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 
   if (tid == 0) {
     mbar_init(bar(B_Q), 2);  // one arrival (with its byte count) per CTA
-    for (int s = 0; s < kPStages; ++s) {
+    for (int s = 0; s < kPKStages; ++s) {
       mbar_init(bar(B_KFULL + s), 2);
-      mbar_init(bar(B_VFULL + s), 2);
       mbar_init(bar(B_KEMPTY + s), 1);
+    }
+    for (int s = 0; s < kPVStages; ++s) {
+      mbar_init(bar(B_VFULL + s), 2);
       mbar_init(bar(B_VEMPTY + s), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -752,61 +794,80 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         tma2_load_4d(q_smem + dh * (128 * 128), &q_map, bar(B_Q) + lead, 0, kv_head * G, dh,
                      q_begin + q0 + (int)rank * tq);
     }
+    // One TMA per lane and 16-token box. The page id of the next block's box is fetched while this
+    // block's loads are issued: a producer that looks up the page table inside the step is slower
+    // than the block time of the rest of the kernel.
     const int32_t* idx = p.kv_indices + ip0;
-    const int n_boxes = 64 / bt;
+    auto page_of = [&](int tok) -> int {
+      if (tok >= kv_hi) return -1;  // nothing to load
+      int page = __ldg(idx + (tok >> ps_log));
+      if (page < 0 || page >= p.num_pages) {
+        record_status(p.status, ST_BAD_PAGE_ID);
+        page = 0;
+      }
+      return page;
+    };
+    const int tok_lane = (int)rank * 64 + lane * 16;  // first token of this lane's box in block 0
+    int page_next = lane < 4 ? page_of(tok_lane) : -1;
+    int s = 0;
+    uint32_t parity = 1;  // the parity of "stage never used": the first pass over the ring does not wait
     for (int j = 0; j < n_blocks; ++j) {
-      const int s = j % kPStages, round = j / kPStages;
       const int t0 = j * kBN + (int)rank * 64;  // this CTA's 64 tokens of the block
-      int live = 0;
-      for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
-      if (round > 0 && !warp_wait(bar(B_KEMPTY + s), (round - 1) & 1, p.status)) break;
-      if (lane == 0) mbar_expect_tx_cluster(bar(B_KFULL + s) + lead, (uint32_t)(live * DH * bt * 128));
+      const int live = min(4, max(0, (kv_hi - t0 + 15) / 16));  // boxes that hold a visible token
+      const int page_now = page_next;
+      if (j + 1 < n_blocks && lane < 4) page_next = page_of(tok_lane + (j + 1) * kBN);
+      if (j >= kPKStages && !warp_wait(bar(B_KEMPTY + s), parity, p.status)) break;
+      if (lane == 0) mbar_expect_tx_cluster(bar(B_KFULL + s) + lead, (uint32_t)(live * 2 * KGROUP));
       __syncwarp();
-      for (int b = lane; b < n_boxes; b += 32) {
-        const int tok = t0 + b * bt;
-        if (tok >= kv_hi) continue;
-        int page = __ldg(idx + (tok >> ps_log));
-        if (page < 0 || page >= p.num_pages) {
-          record_status(p.status, ST_BAD_PAGE_ID);
-          page = 0;
-        }
-        const int in_page = tok & (ps - 1);
-        for (int dh = 0; dh < DH; ++dh)
-          tma2_load_5d(k_smem + (uint32_t)(s * KSTAGE + dh * KHALF + b * bt * 128), &kv_map, bar(B_KFULL + s) + lead, 0,
-                       in_page, kv_head, dh, 2 * page);
+      if (lane < 4 && page_now >= 0) {
+        const int tok = t0 + lane * 16;
+        // coordinates: element, token within its group of 8, head * 2 + half, group of 8 within the page, 2 * page + {K, V}
+        tma2_load_5d(k_smem + (uint32_t)(s * KSTAGE + lane * 2 * KGROUP), &k_map, bar(B_KFULL + s) + lead, 0, 0, 2 * kv_head,
+                     (tok & (ps - 1)) >> 3, 2 * page_now);
+      }
+      if (++s == kPKStages) {
+        s = 0;
+        parity ^= 1;
       }
     }
   } else if (warp == 10) {
     // ================================ the V ring: this CTA's half of head_dim ====================
     const int32_t* idx = p.kv_indices + ip0;
-    const int n_boxes = kBN / bt;
+    const int units = kBN / bt;  // one TMA per lane, page ids fetched one block ahead (see the K ring)
+    auto page_of = [&](int tok) -> int {
+      if (tok >= kv_hi) return -1;
+      int page = __ldg(idx + (tok >> ps_log));
+      if (page < 0 || page >= p.num_pages) {
+        record_status(p.status, ST_BAD_PAGE_ID);
+        page = 0;
+      }
+      return page;
+    };
+    int page_next = lane < units ? page_of(lane * bt) : -1;
+    int s = 0;
+    uint32_t parity = 1;
     for (int j = 0; j < n_blocks; ++j) {
-      const int s = j % kPStages, round = j / kPStages;
       const int t0 = j * kBN;
       const int cols = min(kBN, kv_hi - t0);
       // Rows past the visible length inside the last 16-token step hold whatever the pool left
       // there; 0 * garbage must stay 0, so that block goes through a local barrier, the rows are
       // cleared, and the arrival on CTA 0's barrier is a plain one.
       const bool ragged = (cols & 15) != 0;
-      int live = 0;
-      for (int b = 0; b < n_boxes; ++b) live += (t0 + b * bt < kv_hi) ? 1 : 0;
-      if (round > 0 && !warp_wait(bar(B_VEMPTY + s), (round - 1) & 1, p.status)) break;
+      const int live = (cols + bt - 1) / bt;
+      const int page_now = page_next;
+      if (j + 1 < n_blocks && lane < units) page_next = page_of((j + 1) * kBN + lane * bt);
+      if (j >= kPVStages && !warp_wait(bar(B_VEMPTY + s), parity, p.status)) break;
       const uint32_t full = ragged ? bar(B_VLAST) : bar(B_VFULL + s) + lead;
       if (lane == 0) {
         if (ragged) mbar_expect_tx(full, (uint32_t)(live * bt * 128));
         else mbar_expect_tx_cluster(full, (uint32_t)(live * bt * 128));
       }
       __syncwarp();
-      for (int b = lane; b < n_boxes; b += 32) {
-        const int tok = t0 + b * bt;
-        if (tok >= kv_hi) continue;
-        int page = __ldg(idx + (tok >> ps_log));
-        if (page < 0 || page >= p.num_pages) {
-          record_status(p.status, ST_BAD_PAGE_ID);
-          page = 0;
-        }
-        const int in_page = tok & (ps - 1);
-        tma2_load_5d(v_smem + (uint32_t)(s * VSTAGE + b * bt * 128), &kv_map, full, 0, in_page, kv_head, (int)rank,
+      for (int u = lane; u < units; u += 32) {
+        const int tok = t0 + u * bt;
+        const int page = u < 32 ? page_now : page_of(tok);
+        if (page < 0) continue;
+        tma2_load_5d(v_smem + (uint32_t)(s * VSTAGE + u * bt * 128), &kv_map, full, 0, tok & (ps - 1), kv_head, (int)rank,
                      2 * page + 1);
       }
       if (ragged) {  // only the last block of the item can be ragged: the local barrier is used once
@@ -819,16 +880,22 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_release(bar(B_VFULL + s) + lead);
       }
+      if (++s == kPVStages) {
+        s = 0;
+        parity ^= 1;
+      }
     }
   } else if (warp == 9) {
     // ================================ Q K^T issuer: one thread of CTA 0 ==========================
     if (rank == 0 && lane == 0) {
       bool ok = mbar_wait(bar(B_Q), 0, p.status);
       const uint64_t qd = smem_desc(q_smem, 16, 1024);
-      const uint64_t kd0 = smem_desc(k_smem, 16, 1024);
+      const uint64_t kd0 = smem_desc(k_smem, 16, KGROUP);  // 8-token groups 2 KB apart
+      int s = 0;
+      uint32_t parity = 0;
       for (int j = 0; ok && j < n_blocks; ++j) {
-        const int s = j % kPStages, a = j & 1;
-        ok = mbar_wait(bar(B_KFULL + s), (j / kPStages) & 1, p.status);
+        const int a = j & 1;
+        ok = mbar_wait(bar(B_KFULL + s), parity, p.status);
         // S_a is free once its group has block j-2 in registers
         if (ok && j >= 2) ok = mbar_wait(bar(B_SFREE + a), ((j - 2) >> 1) & 1, p.status);
         if (!ok) break;
@@ -838,12 +905,16 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint64_t qoff = (uint64_t)(((kk >> 2) * (128 * 128) + (kk & 3) * 32) / 16);
-          const uint64_t koff = (uint64_t)(((kk >> 2) * KHALF + (kk & 3) * 32) / 16);
+          const uint64_t koff = (uint64_t)(((kk >> 2) * (8 * 128) + (kk & 3) * 32) / 16);
           if (kk == 0) umma2_ss(d, qd + qoff, kb + koff, IDESC_QK, 0u);
           else umma2_ss_acc(d, qd + qoff, kb + koff, IDESC_QK);
         }
         tc2_commit_both(bar(B_SFULL + a));
         tc2_commit_both(bar(B_KEMPTY + s));
+        if (++s == kPKStages) {
+          s = 0;
+          parity ^= 1;
+        }
       }
     }
   } else if (warp == 11) {
@@ -851,9 +922,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (rank == 0 && lane == 0) {
       const uint64_t vd0 = smem_desc(v_smem, VSTAGE, 1024);
       bool ok = true;
+      int s = 0;
+      uint32_t parity = 0;
       for (int j = 0; ok && j < n_blocks; ++j) {
-        const int s = j % kPStages, a = j & 1;
-        ok = mbar_wait(bar(B_VFULL + s), (j / kPStages) & 1, p.status);
+        const int a = j & 1;
+        ok = mbar_wait(bar(B_VFULL + s), parity, p.status);
         if (ok) ok = mbar_wait(bar(B_PFULL + a), (j >> 1) & 1, p.status);
         if (!ok) break;
         tc_fence_after();
@@ -870,6 +943,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         }
         tc2_commit_both(bar(B_PVDONE + a));  // P_a is free, O holds block j
         tc2_commit_both(bar(B_VEMPTY + s));
+        if (++s == kPVStages) {
+          s = 0;
+          parity ^= 1;
+        }
       }
     }
   } else {
@@ -922,8 +999,16 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       const float m_tile = mx * sc;
       // the reference maximum block j-1 left (the other group's latest), then ours
       float m_prev = -INFINITY;
-      if (j > 0) {  // block j-1 is the other group's ((j-1)/2)-th
-        if (!warp_wait(bar_other, ((j - 1) >> 1) & 1, p.status)) { ok = false; break; }
+      if (j > 0) {
+        // block j-1 is the other group's ((j-1)/2)-th. In the same poll: P_a is free once P V of block
+        // j-2 has read it (long ago, as a rule). Products finish in order, so the other group's pvdone
+        // barrier is then past block j-3 and a wait for block j-1 on it cannot be answered by an older phase.
+        const bool both = j >= 2;
+        if (!warp_wait2(bar_other, ((j - 1) >> 1) & 1, both ? bar(B_PVDONE + a) : bar_other,
+                        both ? ((j - 2) >> 1) & 1 : ((j - 1) >> 1) & 1, p.status)) {
+          ok = false;
+          break;
+        }
         m_prev = mref[(1 - a) * 128 + row];
       }
       float m_new = m_prev;
@@ -937,10 +1022,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         l *= (m_mine == -INFINITY) ? 0.f : exp2f(m_mine - m_new);
         m_mine = m_new;
       }
-      // P_a is free once P V of block j-2 has read it (long ago, as a rule). Products finish in
-      // order, so the other group's barrier is then past block j-3 and a wait for block j-1 on it
-      // cannot be answered by an older phase.
-      if (j >= 2 && !warp_wait(bar(B_PVDONE + a), ((j - 2) >> 1) & 1, p.status)) { ok = false; break; }
       if (j > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
         // O takes in block j-1 until that product has finished
         if (!warp_wait(bar(B_PVDONE + (1 - a)), ((j - 1) >> 1) & 1, p.status)) { ok = false; break; }
@@ -1072,7 +1153,7 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
   std::vector<Item> items, pairs;
   // (the pair kernel is still the slower one on the benchmark shape: opt-in until it is not)
   const char* pairs_env = std::getenv("DESERVE_PREFILL_PAIRS");
-  const bool use_pairs = head_dim == 128 && pairs_env != nullptr && pairs_env[0] == '1';
+  const bool use_pairs = head_dim == 128 && page_size >= 16 && pairs_env != nullptr && pairs_env[0] == '1';
   for (int i = 0; i < batch; ++i) {
     const int n = qo_indptr_host[i + 1] - qo_indptr_host[i];
     const int len = kv_len_host[i];
@@ -1093,7 +1174,15 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
   if (need > plan_capacity_i32)
     return fail(DSV_E_WORKSPACE, "prefill_plan: plan needs %lld int32, capacity %lld", (long long)need,
                 (long long)plan_capacity_i32);
-  auto longest_first = [](const Item& a, const Item& b) { return a.hi > b.hi; };
+  // Most work first, but a request's items stay together: they read the same K/V and then find it in
+  // L2. Requests by their longest item, inside a request the longest item first.
+  std::vector<int> req_hi(batch, 0);
+  for (const Item& it : items) req_hi[it.req] = std::max(req_hi[it.req], it.hi);
+  for (const Item& it : pairs) req_hi[it.req] = std::max(req_hi[it.req], it.hi);
+  auto longest_first = [&](const Item& a, const Item& b) {
+    if (a.req != b.req) return req_hi[a.req] != req_hi[b.req] ? req_hi[a.req] > req_hi[b.req] : a.req < b.req;
+    return a.hi > b.hi;
+  };
   std::stable_sort(items.begin(), items.end(), longest_first);
   std::stable_sort(pairs.begin(), pairs.end(), longest_first);
   plan_host[0] = kPrefillMagic;
@@ -1112,7 +1201,7 @@ int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, 
     int32_t* it = plan_host + kPlanHeader + 4 * k;
     it[0] = src.req; it[1] = src.q0; it[2] = src.nq; it[3] = src.hi;
   }
-  (void)page_size; (void)dtype;
+  (void)dtype;
   return DSV_OK;
 }
 
@@ -1146,13 +1235,14 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
   DSV_REQUIRE(q_stride_tok >= (int64_t)n_q_heads * head_dim && out_stride_tok >= (int64_t)n_q_heads * head_dim,
               "prefill: token stride smaller than a row");
   const int n_items = plan_host[1], n_pairs = plan_host[8];
-  DSV_REQUIRE(n_items >= 0 && n_pairs >= 0 && (n_pairs == 0 || head_dim == 128), "prefill: corrupt plan");
+  DSV_REQUIRE(n_items >= 0 && n_pairs >= 0 && (n_pairs == 0 || (head_dim == 128 && page_size >= 16)), "prefill: corrupt plan");
   if (n_items == 0 && n_pairs == 0) return DSV_OK;
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return fail(DSV_E_CUDA, "prefill: cuTensorMapEncodeTiled is not available");
   const CUtensorMapDataType dt = dtype == DSV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
-  CUtensorMap q_map, kv_map;
+  CUtensorMap q_map, kv_map, k_map, v_map;
+  const bool merged = head_dim == 128 && page_size >= 16;  // 4 KB boxes: both halves of head_dim per 16 tokens
   {  // q: (64 elements, head, 64-element half, token); box = (64, G, 1, 128/G) -> rows token*G + head
     const cuuint64_t dims[4] = {64, (cuuint64_t)n_q_heads, (cuuint64_t)(head_dim / 64), (cuuint64_t)nnz};
     const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)q_stride_tok * 2};
@@ -1172,6 +1262,29 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return fail(DSV_E_CUDA, "prefill: tensor map of the pages rejected");
   }
+  k_map = kv_map;
+  v_map = kv_map;
+  if (merged) {
+    // K boxes of 16 tokens x both halves of head_dim in one 4 KB box. The token index is
+    // split in (token mod 8, token / 8) with the half of head_dim between them, so that the box lands as
+    // [8-token group][half][8 tokens][128 B]: 8-token groups 2 KB apart for either half, which one MMA
+    // descriptor can walk. Dimensions: element, token mod 8, head * 2 + half, token / 8 in the page, 2 * page + {K, V}.
+    const cuuint64_t half_stride = (cuuint64_t)page_size * n_kv_heads * head_dim * 2;
+    const cuuint64_t dims[5] = {64, 8, (cuuint64_t)(2 * n_kv_heads), (cuuint64_t)(page_size / 8), (cuuint64_t)(2 * num_pages)};
+    const cuuint64_t strides[4] = {(cuuint64_t)n_kv_heads * head_dim * 2, 128, (cuuint64_t)8 * n_kv_heads * head_dim * 2,
+                                   half_stride};
+    const cuuint32_t box[5] = {64, 8, 2, 2, 1};
+    if (enc(&k_map, dt, 5, const_cast<void*>(pages_layer), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return fail(DSV_E_CUDA, "prefill: tensor map of the K boxes rejected");
+    // V boxes: the pages' own dimension order with both halves in the box -> [half][16 tokens][128 B]
+    const cuuint64_t vdims[5] = {64, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, 2, (cuuint64_t)(2 * num_pages)};
+    const cuuint64_t vstrides[4] = {(cuuint64_t)n_kv_heads * head_dim * 2, (cuuint64_t)head_dim * 2, 128, half_stride};
+    const cuuint32_t vbox[5] = {64, 16, 1, 2, 1};
+    if (enc(&v_map, dt, 5, const_cast<void*>(pages_layer), vdims, vstrides, vbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return fail(DSV_E_CUDA, "prefill: tensor map of the V boxes rejected");
+  }
   PrefillParams p;
   p.qo_indptr = qo_indptr; p.kv_indices = kv_indices; p.kv_indptr = kv_indptr; p.kv_last_page_len = kv_last_page_len;
   p.out = out; p.items = reinterpret_cast<const int4*>(plan_dev + plan_host[5]);
@@ -1182,26 +1295,35 @@ int dsv_paged_prefill(const void* q, int64_t q_stride_tok, const int32_t* qo_ind
   auto go = [&](auto kernel, dim3 grid, int threads, size_t smem, const PrefillParams& pp) -> cudaError_t {
     cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (er != cudaSuccess) return er;
-    kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(q_map, kv_map, pp);
+    kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(q_map, kv_map, k_map, v_map, pp);
     return cudaGetLastError();
   };
   cudaError_t e = cudaSuccess;
   if (n_pairs > 0) {  // the long items first: a cluster of two CTAs per item and kv head
     PrefillParams pp = p;
     pp.items = reinterpret_cast<const int4*>(plan_dev + plan_host[9]);
-    const size_t smem = (size_t)128 * 128 * 2 + (size_t)kPStages * (2 * 64 * 128 + kBN * 128) + 6 * 128 * 4 + 512 + 1024;
-    const dim3 grid(2u * (unsigned)n_pairs, (unsigned)n_kv_heads);
-    e = dtype == DSV_BF16 ? go(prefill_pair_kernel<__nv_bfloat16>, grid, kPairThreads, smem, pp)
-                          : go(prefill_pair_kernel<__half>, grid, kPairThreads, smem, pp);
+    const size_t smem = (size_t)128 * 128 * 2 + (size_t)kPKStages * (2 * 64 * 128) + (size_t)kPVStages * (kBN * 128) +
+                        6 * 128 * 4 + 512 + 1024;
+    const dim3 grid(2u * (unsigned)n_pairs * (unsigned)n_kv_heads);
+    auto go_pair = [&](auto kernel) -> cudaError_t {
+      cudaError_t er = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (er != cudaSuccess) return er;
+      kernel<<<grid, kPairThreads, smem, (cudaStream_t)stream>>>(q_map, kv_map, k_map, pp);
+      return cudaGetLastError();
+    };
+    e = dtype == DSV_BF16 ? go_pair(prefill_pair_kernel<__nv_bfloat16>) : go_pair(prefill_pair_kernel<__half>);
   }
   if (e == cudaSuccess && n_items > 0) {
     const size_t smem = (size_t)2 * 128 * head_dim * 2 + (size_t)(2 + kVStages) * kBN * head_dim * 2 + 256 + 1024;
-    const dim3 grid((unsigned)n_items, (unsigned)n_kv_heads);
+    const dim3 grid((unsigned)n_items * (unsigned)n_kv_heads);
     if (dtype == DSV_BF16)
-      e = head_dim == 128 ? go(prefill_kernel<__nv_bfloat16, 128>, grid, kThreads, smem, p)
-                          : go(prefill_kernel<__nv_bfloat16, 64>, grid, kThreads, smem, p);
+      e = merged ? go(prefill_kernel<__nv_bfloat16, 128, true>, grid, kThreads, smem, p)
+                 : head_dim == 128 ? go(prefill_kernel<__nv_bfloat16, 128, false>, grid, kThreads, smem, p)
+                                   : go(prefill_kernel<__nv_bfloat16, 64, false>, grid, kThreads, smem, p);
     else
-      e = head_dim == 128 ? go(prefill_kernel<__half, 128>, grid, kThreads, smem, p) : go(prefill_kernel<__half, 64>, grid, kThreads, smem, p);
+      e = merged ? go(prefill_kernel<__half, 128, true>, grid, kThreads, smem, p)
+                 : head_dim == 128 ? go(prefill_kernel<__half, 128, false>, grid, kThreads, smem, p)
+                                   : go(prefill_kernel<__half, 64, false>, grid, kThreads, smem, p);
   }
   if (e != cudaSuccess) return fail(DSV_E_CUDA, "prefill launch failed: %s", cudaGetErrorString(e));
   return DSV_OK;

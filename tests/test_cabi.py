@@ -141,7 +141,16 @@ def test_prefill_plan_tiles_every_new_token_once(causal, monkeypatch):
             cover[req][q0 : q0 + nq] += 1
             n = qo[req + 1] - qo[req]
             assert hi == (kv_len[req] - n + q0 + nq if causal else kv_len[req])
-        assert (np.diff(items[:, 3]) <= 0).all()  # most work first
+        # most work first, a request's items together (they read the same K/V): requests by their longest
+        # item over both lists, inside a request the longest item first
+        reqs = items[:, 0].tolist()
+        order = [r for k, r in enumerate(reqs) if k == 0 or reqs[k - 1] != r]
+        assert len(order) == len(set(order))
+        every = np.concatenate([singles, pairs])
+        longest = {int(r): int(every[every[:, 0] == r][:, 3].max()) for r in set(every[:, 0].tolist())}
+        assert all(longest[x] >= longest[y] for x, y in zip(order, order[1:]))
+        for r in order:
+            assert (np.diff(items[items[:, 0] == r][:, 3]) <= 0).all()
     assert all((c == 1).all() for c in cover)
     assert n_pairs == 11 and n_items == 1  # 100 -> 64 + 36; 1 -> a single; 512 -> 8 x 64; 37 -> one pair
 
