@@ -1062,6 +1062,30 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
                              "the step's tokens go back to pinned host memory and the host waits for them before the "
                              "next step (one microbatch; on one GPU the microbatches run one after the other, so its "
                              "rate is the job's)"}
+    # ---- N > 1: the same job with the serving loop's host round trip on the first stage -----------
+    if world > 1 and not args.no_e2e:
+        main_tokens = res.pop("tokens", None)
+        res.pop("stage", None)
+        gc.collect()
+        torch.cuda.empty_cache()
+        import dataclasses
+
+        cfg_e = dataclasses.replace(cfg, host_tokens=True)
+        COUNTERS["h2d_bytes"] = 0
+        r1 = run_stage(rank, world, cfg_e, dev, dist, stage=stage)
+        t1 = torch.tensor([r1["decode_ms"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t1, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t1[0])
+        if rank == 0:
+            slots_all = max(cfg.steps * M, 1)
+            out["e2e"] = {"value": M * S * K / (e2e_ms * 1e-3), "unit": "tok/s",
+                          "h2d_bytes_per_step": int(M * (S * 4 + COUNTERS["h2d_bytes"] // slots_all)),
+                          "d2h_bytes_per_step": int(M * S * 4), "ms_per_step": e2e_ms / max(K, 1),
+                          "tokens_equal_device_loop": bool(torch.equal(r1["tokens"], main_tokens)),
+                          "api": "StageProcessor.process_step per microbatch slot on every stage: on the first stage the "
+                                 "step's tokens (finished from the last stage's message) go to pinned host memory, the "
+                                 "host waits for them, and the next step's token ids come from there; bytes are the "
+                                 "first stage's, per decode step of all microbatches"}
     status = _lib.read_device_status()
     if status != 0:
         raise SystemExit(f"device self-check fired: status {status}")
@@ -1096,6 +1120,9 @@ def run_ours(args):
         return
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    from deserve_b200.pinned import bind_host_to_gpu
+
+    host_binding = bind_host_to_gpu(local)  # before any pinned allocation: swap images on the GPU's NUMA node
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -1147,6 +1174,7 @@ def run_ours(args):
                 line["e2e"] = kv["e2e"]
             if pipe_error:
                 line["pipeline_error"] = pipe_error
+        line["host_binding"] = host_binding
         if kv is not None:
             line["kv_step"] = kv
         if roof is not None:

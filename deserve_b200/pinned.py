@@ -65,3 +65,37 @@ def ring(name: str, slots: int = 8, capacity: int = 1 << 14) -> PinnedRing:
     if r is None:
         r = _RINGS[name] = PinnedRing(slots, capacity)
     return r
+
+
+def bind_host_to_gpu(device_index: int) -> dict:
+    """Restrict this process to the CPUs NVML reports as local to the GPU, so that the pinned buffers it
+    allocates afterwards (swap images, descriptor rings) and the threads that feed the GPU sit on the GPU's
+    NUMA node. On a two-socket host with eight GPUs every rank otherwise allocates wherever it happens to
+    run, and the region DMA of all ranks shares one socket's memory and the link between the sockets.
+    Changes nothing outside this process (its own CPU affinity mask); returns what it did for the record.
+    A host without NVML, or a mask that leaves no CPU of the current one, is left alone."""
+    import os
+
+    info = {"bound": False}
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = int(visible.split(",")[device_index]) if visible else device_index
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (max(os.cpu_count() or 1, 1) + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        local = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus = local & allowed
+        info.update(local_cpus=len(local), allowed_cpus=len(allowed))
+        if cpus and cpus != allowed:
+            os.sched_setaffinity(0, cpus)
+            info.update(bound=True, cpus=len(cpus))
+        elif cpus:
+            info.update(cpus=len(cpus), note="already local")
+    except Exception as exc:  # no NVML, no permission, a single-node host: nothing to do
+        info["note"] = repr(exc)[:120]
+    return info
+

@@ -52,7 +52,7 @@ class PipelineConfig:
     output_gain: float = 1.0      # multiplies the output projection (tests use decisive logits)
     concurrent: int | None = None  # microbatches in flight at once (a wave); None = all of them
     warmup_tokens: int = 0        # decode steps of every wave that run before its timed region
-    host_tokens: bool = False     # one stage only: every step's tokens go to pinned host memory and the next
+    host_tokens: bool = False     # every step's tokens go to pinned host memory (first stage) and the next
     #                               step's input comes back from there (the serving loop a client sees)
     extra: dict = field(default_factory=dict)
 
@@ -147,7 +147,6 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
     assert a.n_layers % world == 0 and M % Mw == 0 and Mw >= world, "layers / microbatches must split evenly"
     # one microbatch alone cannot rotate through two swap regions (there is nobody to swap with)
     assert Mw > 1 or cfg.swap_pages == 0, "a single microbatch in flight needs swap_pages = 0"
-    assert not cfg.host_tokens or world == 1, "host_tokens is the one-stage serving loop"
     lb, le = rank * a.n_layers // world, (rank + 1) * a.n_layers // world
     if stage is None:
         stage = make_stage(a, rank, world, device, cfg.dtype, cfg.seed, cfg.output_gain)
@@ -204,7 +203,16 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
                 # the last stage's message of step s-1: normed rows + its half of the head; finish the tokens
                 with phase("finish_head"):
                     x = stage.finish_head(x)
-                pending.append((m, s - 1, x))
+                if cfg.host_tokens:
+                    # serving loop over several stages: the client reads the step's tokens from pinned host memory
+                    # and the next step's input comes from there (the host waits for the copy)
+                    with phase("tokens_to_host"):
+                        h = host_ring[n_host[0] % len(host_ring)][: x.numel()]
+                        n_host[0] += 1
+                        h.copy_(x, non_blocking=True)
+                        torch.cuda.current_stream(device).synchronize()
+                    x = h  # pinned; stays intact until Mw + 1 further steps have passed
+                pending.append((m, s - 1, x.clone() if cfg.host_tokens else x))
             req = StepRequest(microbatch_id=m, xs=x)
             if s < P:
                 sel = subset(s)
@@ -229,7 +237,7 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
             proc.synchronize()
             _, result = proc.process_step(req)
             y = result.ongoing_xs  # activations; on the last stage the packed partial head
-            if cfg.host_tokens:
+            if cfg.host_tokens and world == 1:
                 with phase("tokens_to_host"):
                     toks = stage.finish_head(y)  # one stage: finish at once, the client reads the tokens now
                     h = host_ring[n_host[0] % len(host_ring)][: toks.numel()]
@@ -272,7 +280,7 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
         stats["launches_timed"] += _lib.LAUNCHES[0] - launches0  # this package's kernels inside the timed region
         in_timed[0] = False
         pipe.advance(world - 1)  # the last units of the later stages
-        if not cfg.host_tokens:  # the tokens of the last step: the first stage finishes the last stage's partial heads
+        if not (cfg.host_tokens and world == 1):  # the last step's tokens: the first stage finishes the last stage's partial heads
             for m, packed in enumerate(pipe.take_finals()):
                 pending.append((m, cfg.steps - 1, stage.finish_head(packed)))
         pipe.flush()
@@ -326,6 +334,9 @@ def main() -> None:
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    from .pinned import bind_host_to_gpu
+
+    bind_host_to_gpu(local)  # before the pinned swap images are allocated
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:

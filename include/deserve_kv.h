@@ -193,6 +193,11 @@ int dsv_paged_decode(const void* q, int64_t q_stride_tok, const void* pages_laye
  * last token sees (all of them when causal = 0). Requests with fewer than
  * min_new_tokens new tokens get no work item (a caller that sends the decode
  * rows of a mixed batch to dsv_paged_decode passes 2). Pure host arithmetic.
+ * The plan is opaque to the caller: a 12-integer header, then the items (four
+ * integers each) of the single-CTA kernel and those of the two-CTA kernel; the
+ * latter list is empty unless the environment holds DESERVE_PREFILL_PAIRS=1
+ * (head_dim 128, pages of 16 tokens or more). Items run the longest request
+ * first, a request's items together.
  */
 int dsv_prefill_plan(const int32_t* qo_indptr_host, const int32_t* kv_len_host, int batch,
                      int n_q_heads, int n_kv_heads, int head_dim, int page_size, int dtype,

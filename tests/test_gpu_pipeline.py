@@ -119,6 +119,8 @@ def _worker(rank, world, port, q):
     res = run_stage(rank, world, _cfg(world), dev, dist)
     # more microbatches than stages: four in flight on two stages, then two waves of two
     many = [run_stage(rank, world, _cfg_many(c), dev, dist) for c in (4, 2)]
+    # the serving loop over two stages: the first stage passes every step's tokens through pinned host memory
+    many.append(run_stage(rank, world, _cfg_many(4, host_tokens=True), dev, dist))
     if rank == 0:  # the first stage finishes the split output head, so the tokens are there
         q.put((res["tokens"].clone(), [m["tokens"].clone() for m in many]))
     dist.barrier()
@@ -149,5 +151,5 @@ def test_two_stage_pipeline_matches_one_stage_and_dense():
     res = run_stage(0, 1, _cfg(1), torch.device("cuda:0"))
     assert torch.equal(res["tokens"][0], tokens2[0]), "stage split changed the greedy tokens"
     one_gpu = run_stage(0, 1, _cfg_many(1), torch.device("cuda:0"))["tokens"]
-    for got in many2:  # four microbatches on two stages, all in flight or in two waves: the one-GPU tokens
+    for got in many2:  # four microbatches on two stages, all in flight, in two waves, or with host tokens: the one-GPU tokens
         assert torch.equal(got, one_gpu), "stage split / waves changed the greedy tokens"

@@ -313,3 +313,16 @@ def test_kvconfig_builds_the_stage_objects_and_ownership_check_finds_planted_fau
     b.pool._bitmap[5] = True                                         # plant: an owned page marked free
     with pytest.raises(AssertionError, match="marked free"):
         dk.check_page_ownership(pool, [b])
+
+
+def test_bind_host_to_gpu_leaves_the_process_alone_without_nvml():
+    import os
+
+    from deserve_b200.pinned import bind_host_to_gpu
+
+    before = os.sched_getaffinity(0)
+    info = bind_host_to_gpu(0)
+    assert isinstance(info, dict) and "bound" in info
+    if not info["bound"]:
+        assert os.sched_getaffinity(0) == before
+    os.sched_setaffinity(0, before)
