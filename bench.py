@@ -1021,6 +1021,9 @@ def pipeline_bench(args, dk, rank, world, local, dev, dist):
                 "mean_pages_out_per_slot": res["swap_pages_out"] / max(res["swap_slots"], 1),
                 "mean_pages_in_per_slot": res["swap_pages_in"] / max(res["swap_slots"], 1),
                 "max_pages_out_per_slot": res["swap_pages_out_max"],
+                "mean_token_rows_out_per_page": res["swap_rows_out"] / max(res["swap_slots"], 1),
+                "mean_token_rows_in_per_page": res["swap_rows_in"] / max(res["swap_slots"], 1),
+                "rows_note": "of a travelling page (16 token rows of K, 16 of V) only the rows that hold tokens move",
                 "dma_out_ms_per_slot": res["swap_dma_out_ms"] / max(res["swap_dma_slots"], 1),
                 "dma_in_ms_per_slot": res["swap_dma_in_ms"] / max(res["swap_dma_slots"], 1),
                 "dma_note": "time the region copies of one slot run on their side streams (device events); they start "

@@ -92,7 +92,7 @@ _SIGNATURES = {
     "dsv_swap_in_pages": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "dsv_region_swap": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
-                                c_void_p, c_void_p, c_void_p]),
+                                c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32]),
 }
 
 for _name, (_res, _args) in _SIGNATURES.items():

@@ -73,6 +73,11 @@ def build_step(task_datas: list[TaskData], kvcaches: list[PagedKVCache], buf: np
     _lib.check(rc)
     sizes = (bsz + 1, bsz + 1, bsz, bsz, bsz, n_idx)
     views = {n: buf[int(o) : int(o) + sz] for n, o, sz in zip(_NAMES, offs[:6], sizes)}
+    if getattr(pool, "rows_used", None) is not None and n_idx:
+        # the swap regions learn how many token rows of their pages this step's requests fill
+        kvp, idx = views["kv_page_indptr"], views["kv_page_indices"]
+        has = kvp[1:] > kvp[:-1]
+        pool.note_rows(idx, idx[kvp[1:][has] - 1], views["kv_last_page_lens"][has])
     return buf, int(offs[6]), views
 
 

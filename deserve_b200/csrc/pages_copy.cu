@@ -246,7 +246,8 @@ int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_str
 
 int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes,
                     int64_t region_offset_bytes, int64_t region_bytes, int64_t out_bytes, int64_t in_bytes,
-                    void* host_out, const void* host_in, void* stream_out, void* stream_in, void* event) {
+                    void* host_out, const void* host_in, void* stream_out, void* stream_in, void* event,
+                    int64_t page_bytes, int32_t page_size, int32_t out_rows, int32_t in_rows) {
   using namespace dsv;
   DSV_REQUIRE(num_layers >= 0 && region_bytes >= 0, "region_swap: negative size");
   DSV_REQUIRE(out_bytes >= 0 && out_bytes <= region_bytes && in_bytes >= 0 && in_bytes <= region_bytes,
@@ -263,25 +264,50 @@ int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes
   DSV_REQUIRE(!both || event != nullptr, "region_swap: an event is needed when both directions are given");
   unsigned char* dev = static_cast<unsigned char*>(pages_base) + region_offset_bytes;
   cudaStream_t s_out = (cudaStream_t)stream_out, s_in = (cudaStream_t)stream_in;
+  // A page is [K: page_size token rows][V: page_size token rows]. When no page of the travelling head
+  // holds more than `rows` tokens, only the first `rows` rows of every half travel: a 2-D copy whose
+  // lines are the halves (pitch = half a page, the same on both sides, so the host image keeps the
+  // region's layout). rows = page_size (or page_bytes = 0) is the plain contiguous copy.
+  const bool by_rows = page_bytes > 0 && page_size > 0;
+  DSV_REQUIRE(!by_rows || (page_bytes % (2 * (int64_t)page_size) == 0 && out_rows >= 0 && out_rows <= page_size &&
+                           in_rows >= 0 && in_rows <= page_size && out_bytes % page_bytes == 0 && in_bytes % page_bytes == 0),
+              "region_swap: rows (%d out, %d in) must lie in [0, page_size = %d] and the byte counts be whole pages",
+              out_rows, in_rows, page_size);
+  const int64_t half_bytes = by_rows ? page_bytes / 2 : 0, row_bytes = by_rows ? half_bytes / page_size : 0;
+  const bool out_2d = by_rows && out_rows < page_size, in_2d = by_rows && in_rows < page_size;
+  if (out_2d && out_rows == 0) out_bytes = 0;
+  if (in_2d && in_rows == 0) in_bytes = 0;
+  if (out_bytes == 0 && in_bytes == 0) return DSV_OK;
+  const bool edge = out_bytes > 0 && in_bytes > 0;
   // groups of layers: one event edge per group keeps the number of API calls low
   const int group = std::max(1, (num_layers + 7) / 8);
   for (int l0 = 0; l0 < num_layers; l0 += group) {
     const int l1 = std::min(num_layers, l0 + group);
     if (out_bytes > 0) {
-      for (int l = l0; l < l1; ++l)
-        DSV_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(host_out) + (int64_t)l * region_bytes,
-                                 dev + (int64_t)l * layer_stride_bytes, (size_t)out_bytes, cudaMemcpyDeviceToHost,
-                                 s_out));
-      if (both) {
+      for (int l = l0; l < l1; ++l) {
+        unsigned char* h = static_cast<unsigned char*>(host_out) + (int64_t)l * region_bytes;
+        const unsigned char* d = dev + (int64_t)l * layer_stride_bytes;
+        if (out_2d)
+          DSV_CUDA(cudaMemcpy2DAsync(h, (size_t)half_bytes, d, (size_t)half_bytes, (size_t)(out_rows * row_bytes),
+                                     (size_t)(out_bytes / half_bytes), cudaMemcpyDeviceToHost, s_out));
+        else
+          DSV_CUDA(cudaMemcpyAsync(h, d, (size_t)out_bytes, cudaMemcpyDeviceToHost, s_out));
+      }
+      if (edge) {
         DSV_CUDA(cudaEventRecord((cudaEvent_t)event, s_out));
         DSV_CUDA(cudaStreamWaitEvent(s_in, (cudaEvent_t)event, 0));
       }
     }
     if (in_bytes > 0) {
-      for (int l = l0; l < l1; ++l)
-        DSV_CUDA(cudaMemcpyAsync(dev + (int64_t)l * layer_stride_bytes,
-                                 static_cast<const unsigned char*>(host_in) + (int64_t)l * region_bytes,
-                                 (size_t)in_bytes, cudaMemcpyHostToDevice, s_in));
+      for (int l = l0; l < l1; ++l) {
+        unsigned char* d = dev + (int64_t)l * layer_stride_bytes;
+        const unsigned char* h = static_cast<const unsigned char*>(host_in) + (int64_t)l * region_bytes;
+        if (in_2d)
+          DSV_CUDA(cudaMemcpy2DAsync(d, (size_t)half_bytes, h, (size_t)half_bytes, (size_t)(in_rows * row_bytes),
+                                     (size_t)(in_bytes / half_bytes), cudaMemcpyHostToDevice, s_in));
+        else
+          DSV_CUDA(cudaMemcpyAsync(d, h, (size_t)in_bytes, cudaMemcpyHostToDevice, s_in));
+      }
     }
   }
   return DSV_OK;

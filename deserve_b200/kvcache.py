@@ -175,6 +175,10 @@ class PagePool:
         with self.mutex:
             self.num_avails += len(ids)
             self._bitmap[ids] = True
+            rows = getattr(self, "rows_used", None)
+            if rows is not None and len(ids):  # whoever gets a swap-region page next holds whole pages until told otherwise
+                reg = ids[ids >= self.num_pages_main] - self.num_pages_main
+                rows[reg] = self.page_size
 
     def retrieve(self, indices) -> torch.Tensor:
         idx = torch.as_tensor(_as_ids(indices), device=self.pages.device)
@@ -311,6 +315,8 @@ class CopiedPinnedMemory(PinnedMemory):
         super().__init__(size, dtype)
         self.bitmap = np.ones(num_pages_swap, dtype=bool)
         self.count = num_pages_swap
+        # token rows in use per page of the image (None = unknown: whole pages travel); written by swap2
+        self.rows = None
 
 
 # --------------------------------------------------------------------------
@@ -346,6 +352,10 @@ class VirtualPagePool(GpuPagePool):
         self.on = 0
         self.live_only = True            # swap2 moves only the head of a region that is in use
         self.last_swap_pages = (0, 0)    # pages per layer the last swap2 moved (out, in)
+        self.last_swap_rows = (page_size, page_size)  # token rows of each half page it moved (out, in)
+        # token rows that carry data, per page of the two regions (page_size = the whole page: the state of a
+        # page nobody has described yet); the step builder lowers it for the pages it describes (note_rows)
+        self.rows_used: np.ndarray | None = np.full(2 * s, page_size, dtype=np.int32) if s > 0 else None
         self.dma_events: list | None = None  # set to [] to collect (out start, out end, in start, in end) timing events
         if _is_cuda(self.main_device):
             self.stream = torch.cuda.Stream(device=self.main_device)   # outgoing DMA
@@ -384,6 +394,28 @@ class VirtualPagePool(GpuPagePool):
         self.swap_count = from_memory.count
         return self.slices[1 - self.on]
 
+    def note_rows(self, page_ids: np.ndarray, tails: np.ndarray, tail_rows: np.ndarray) -> None:
+        """Called by the step builder: the pages a step's requests hold (`page_ids`, full but for each
+        request's last page `tails`, which holds `tail_rows` tokens). Keeps, per page of the swap regions,
+        how many token rows carry data, so that swap2 moves only those rows of each half page."""
+        if self.rows_used is None:
+            return
+        main = self.num_pages_main
+        reg = page_ids[page_ids >= main]
+        if reg.size:
+            self.rows_used[reg - main] = self.page_size
+        sel = tails >= main
+        if sel.any():
+            self.rows_used[tails[sel] - main] = tail_rows[sel]
+
+    def _rows_of(self, lo: int, n_pages: int, free_bitmap) -> int:
+        """Most token rows any page in use among the first n_pages of the region at page `lo` holds."""
+        if self.rows_used is None or n_pages == 0:
+            return self.page_size
+        used = ~np.asarray(free_bitmap[:n_pages], dtype=bool)
+        rows = self.rows_used[lo - self.num_pages_main : lo - self.num_pages_main + n_pages][used]
+        return int(rows.max()) if rows.size else 0
+
     @staticmethod
     def _live_pages(free_bitmap) -> int:
         """Pages of a region that have to travel: everything up to the highest page in
@@ -401,12 +433,25 @@ class VirtualPagePool(GpuPagePool):
         contents of free pages are never read, so leaving them behind changes no
         result. Set `live_only = False` for the reference's exact byte movement."""
         lo, hi = self._handoff(from_memory, to_memory)
+        rows_out = rows_in = self.page_size
         if self.live_only:
             n_out, n_in = self._live_pages(to_memory.bitmap), self._live_pages(self._swap_bitmap)
+            if self.rows_used is not None:
+                # of the pages that travel, only the token rows that hold data: the outgoing image remembers
+                # its pages' rows, the incoming one brings its own back into this region's slots
+                rel = lo - self.num_pages_main
+                rows_out = self._rows_of(lo, n_out, to_memory.bitmap)
+                to_memory.rows = self.rows_used[rel : rel + (hi - lo)].copy()
+                if from_memory.rows is not None:
+                    self.rows_used[rel : rel + (hi - lo)] = from_memory.rows
+                    rows_in = self._rows_of(lo, n_in, self._swap_bitmap)
+                else:
+                    self.rows_used[rel : rel + (hi - lo)] = self.page_size
         else:
             n_out = n_in = hi - lo
         self.last_swap_pages = (n_out, n_in)
-        self._region_dma(lo, hi, to_memory.memory, from_memory.memory, n_out, n_in)
+        self.last_swap_rows = (rows_out, rows_in)
+        self._region_dma(lo, hi, to_memory.memory, from_memory.memory, n_out, n_in, rows_out, rows_in)
 
     def swap(self, from_memory: CopiedPinnedMemory, to_memory: CopiedPinnedMemory) -> None:
         """Same data movement as swap2; the reference's torch statement of it
@@ -418,7 +463,8 @@ class VirtualPagePool(GpuPagePool):
         self._region_dma(lo, hi, to_memory.memory, from_memory.memory)
 
     def _region_dma(self, lo: int, hi: int, host_out: torch.Tensor, host_in: torch.Tensor,
-                    n_out: int | None = None, n_in: int | None = None) -> None:
+                    n_out: int | None = None, n_in: int | None = None, rows_out: int | None = None,
+                    rows_in: int | None = None) -> None:
         _lib.require_cuda(self.pages)
         n_out = hi - lo if n_out is None else n_out
         n_in = hi - lo if n_in is None else n_in
@@ -438,7 +484,9 @@ class VirtualPagePool(GpuPagePool):
         _lib.check(_lib.lib.dsv_region_swap(
             self.pages.data_ptr(), self.num_layers, self.layer_stride_bytes, lo * self.page_bytes,
             (hi - lo) * self.page_bytes, n_out * self.page_bytes, n_in * self.page_bytes, host_out.data_ptr(),
-            host_in.data_ptr(), self.stream.cuda_stream, self.stream2.cuda_stream, self._edge.cuda_event))
+            host_in.data_ptr(), self.stream.cuda_stream, self.stream2.cuda_stream, self._edge.cuda_event,
+            self.page_bytes, self.page_size, self.page_size if rows_out is None else rows_out,
+            self.page_size if rows_in is None else rows_in))
         if timing is not None:
             timing[1].record(self.stream)
             timing[3].record(self.stream2)

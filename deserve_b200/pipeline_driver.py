@@ -173,7 +173,8 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
                  if cfg.host_tokens else None)
     stats = {"prefill_ms": 0.0, "decode_ms": 0.0, "decode_compute_ms": 0.0, "pages_free_min": pool.num_avails,
              "swap_pages_out": 0, "swap_pages_in": 0, "swap_slots": 0, "swap_pages_out_max": 0, "slots_timed": 0,
-             "launches_timed": 0, "swap_dma_out_ms": 0.0, "swap_dma_in_ms": 0.0, "swap_dma_slots": 0}
+             "launches_timed": 0, "swap_dma_out_ms": 0.0, "swap_dma_in_ms": 0.0, "swap_dma_slots": 0,
+             "swap_rows_out": 0, "swap_rows_in": 0}
 
     def subset(s):
         return list(range(s * c, min(S, (s + 1) * c)))
@@ -256,6 +257,8 @@ def run_stage(rank: int, world: int, cfg: PipelineConfig, device: torch.device, 
                     stats["swap_pages_out"] += o
                     stats["swap_pages_in"] += i_
                     stats["swap_pages_out_max"] = max(stats["swap_pages_out_max"], o)
+                    stats["swap_rows_out"] += pool.last_swap_rows[0]
+                    stats["swap_rows_in"] += pool.last_swap_rows[1]
                     stats["swap_slots"] += 1
             return y
 

@@ -328,11 +328,18 @@ int dsv_swap_in_pages(const void* host_pool, void* pages_base, int64_t layer_str
  * copy has finished (`event`, a cudaEvent_t of the caller, carries the edge), so
  * both directions of the host link are busy at once. host_out or host_in may be
  * NULL to skip that direction. Bit-exact. Asynchronous: wait on both streams.
+ * A page is [K: page_size token rows][V: page_size token rows]; out_rows /
+ * in_rows < page_size move only the first rows of every half of the travelling
+ * pages (for a caller that knows that no page of the head holds more tokens:
+ * the tail pages of sequences that grow a token per step), as a 2-D copy that
+ * keeps the region's layout in the host image. page_bytes = 0 or rows =
+ * page_size: whole pages.
  */
 int dsv_region_swap(void* pages_base, int num_layers, int64_t layer_stride_bytes,
                     int64_t region_offset_bytes, int64_t region_bytes, int64_t out_bytes,
                     int64_t in_bytes, void* host_out, const void* host_in, void* stream_out,
-                    void* stream_in, void* event);
+                    void* stream_in, void* event, int64_t page_bytes, int32_t page_size,
+                    int32_t out_rows, int32_t in_rows);
 
 /*
  * The host half of a step in one native call (no CUDA): for every request of

@@ -36,11 +36,15 @@ def test_invalid_arguments_return_codes_not_crashes():
     assert "dtype" in _lib.last_error()
     # nothing to do is not an error
     assert L.dsv_append_paged_kv(None, None, 0, 0, None, None, 0, 4, None, None, None, 0, 0, 8, 128, 16, 2, None) == 0
-    assert L.dsv_region_swap(None, 4, 1024, 512, 1024, 1024, 1024, None, None, None, None, None) == 0  # both directions skipped
+    assert L.dsv_region_swap(None, 4, 1024, 512, 1024, 1024, 1024, None, None, None, None, None, 0, 0, 0, 0) == 0  # both directions skipped
     buf = (ctypes.c_char * 64)()
-    assert L.dsv_region_swap(buf, 4, 1024, 512, 1024, 1024, 0, buf, None, None, None, None) == -1
+    assert L.dsv_region_swap(buf, 4, 1024, 512, 1024, 1024, 0, buf, None, None, None, None, 0, 0, 0, 0) == -1
     assert "outside a layer" in _lib.last_error()
-    assert L.dsv_region_swap(buf, 4, 4096, 512, 1024, 2048, 0, buf, None, None, None, None) == -1
+    # rows beyond the page, or byte counts that are not whole pages, are refused before any copy
+    assert L.dsv_region_swap(buf, 4, 4096, 512, 1024, 1024, 0, buf, None, None, None, None, 512, 16, 17, 0) == -1
+    assert L.dsv_region_swap(buf, 4, 4096, 512, 1024, 768, 0, buf, None, None, None, None, 512, 16, 4, 0) == -1
+    assert "whole pages" in _lib.last_error()
+    assert L.dsv_region_swap(buf, 4, 4096, 512, 1024, 2048, 0, buf, None, None, None, None, 0, 0, 0, 0) == -1
     assert "out_bytes" in _lib.last_error()
     assert L.dsv_pack_pages(buf, 1024, 100, 4, buf, buf, 1, 1, 0, 1, buf, None) == -1
     assert "multiple of 16" in _lib.last_error()

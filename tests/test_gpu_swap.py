@@ -61,6 +61,43 @@ def test_region_swap_bit_exact(dtype, layers, whole):
     assert torch.equal(pool.pages.cpu().view(torch.uint8), ref.view(torch.uint8))
 
 
+def test_region_swap_moves_only_the_token_rows_in_use():
+    """The step builder tells the pool how many token rows of its region pages hold data (note_rows);
+    swap2 then moves only those rows of each half page (K rows, V rows), both ways, and the row counts
+    travel with the host image. Everything else stays as it was on both sides."""
+    layers, main, swap, ps, hkv, d, dtype = 3, 6, 4, 16, 2, 64, torch.bfloat16
+    pool = dk.VirtualPagePool(layers, main, swap, ps, DEV, dtype, n_kv_heads=hkv, head_dim=d)
+    ref = _fill(pool, 3)
+    size = pool.calc_swap_size()
+    prev_mb = dk.CopiedPinnedMemory(size, swap, DEV, dtype)
+    next_mb = dk.CopiedPinnedMemory(size, swap, DEV, dtype)
+    incoming = torch.randn(size, generator=torch.Generator().manual_seed(4)).to(dtype)
+    next_mb.memory.copy_(incoming)
+    prev_mb.memory.zero_()
+    lo, hi = pool.slices[1 - pool.on]
+    pool._swap_bitmap[:2] = False                 # going out: pages 0 and 1 in use, holding 5 and 3 tokens
+    pool.note_rows(np.array([lo, lo + 1]), np.array([lo, lo + 1]), np.array([5, 3]))
+    next_mb.bitmap[[0, 2]] = False                # coming in: pages 0 and 2 in use, 7 and 2 tokens; page 1 is free
+    next_mb.rows = np.array([7, 16, 2, 16], dtype=np.int32)
+    pool.swap2(next_mb, prev_mb)
+    assert pool.last_swap_pages == (2, 3) and pool.last_swap_rows == (5, 7)
+    assert prev_mb.rows.tolist() == [5, 3, 16, 16]
+    rel = lo - main
+    assert pool.rows_used[rel : rel + swap].tolist() == [7, 16, 2, 16]
+    pool.stream.synchronize()
+    pool.stream2.synchronize()
+    # pages are [K|V][token][head][dim]: rows = tokens of each half
+    shape = (layers, swap, 2, ps, hkv, d)
+    want_out = torch.zeros(shape, dtype=dtype)
+    want_out[:, :2, :, :5] = ref[:, lo : lo + 2, :, :5]
+    assert torch.equal(prev_mb.memory.view(torch.uint8), want_out.view(-1).view(torch.uint8))
+    ref[:, lo : lo + 3, :, :7] = incoming.view(shape)[:, :3, :, :7]
+    assert torch.equal(pool.pages.cpu().view(torch.uint8), ref.view(torch.uint8))
+    # a page that is freed is a whole page again for whoever gets it next
+    pool.free(np.array([lo]))
+    assert pool.rows_used[rel] == ps
+
+
 def test_region_state_machine_with_data_follows_a_microbatch():
     """Two microbatches share one pool: each one's swap-region pages leave to its
     pinned buffer while the other computes and come back intact (rounds = 3, so
