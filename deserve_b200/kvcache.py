@@ -410,7 +410,9 @@ class VirtualPagePool(GpuPagePool):
 
     def _rows_of(self, lo: int, n_pages: int, free_bitmap) -> int:
         """Most token rows any page in use among the first n_pages of the region at page `lo` holds."""
-        if self.rows_used is None or n_pages == 0:
+        if n_pages == 0:
+            return 0
+        if self.rows_used is None:
             return self.page_size
         used = ~np.asarray(free_bitmap[:n_pages], dtype=bool)
         rows = self.rows_used[lo - self.num_pages_main : lo - self.num_pages_main + n_pages][used]

@@ -326,3 +326,38 @@ def test_bind_host_to_gpu_leaves_the_process_alone_without_nvml():
     if not info["bound"]:
         assert os.sched_getaffinity(0) == before
     os.sched_setaffinity(0, before)
+
+
+def test_swap_regions_learn_the_token_rows_of_their_pages_from_the_step_builder():
+    """A pool with swap regions keeps, per region page, how many token rows hold data: the step builder
+    lowers it for the pages a step describes (a request's last page holds kv_last_page_len rows, the others
+    are full), a freed page counts as whole again, and the count of a region's head is the most any page in
+    use holds. swap2 moves only that many rows of each half page."""
+    from deserve_b200.context import pack_descriptors
+    from deserve_b200.task import TaskData
+
+    ps, main, swap = 8, 2, 3
+    pool = dk.VirtualPagePool(1, main, swap, ps, CPU, torch.float16, n_kv_heads=1, head_dim=8)
+    pta = dk.PageTableAllocator(4, 64, ps, CPU)
+    assert pool.rows_used.tolist() == [ps] * (2 * swap)
+    cache = dk.VirtualPagedKVCache.empty(pta, pool)
+    task = TaskData.empty("t", 19, dk.SamplingParams()) if hasattr(TaskData, "empty") else None
+    if task is None:
+        pytest.skip("TaskData.empty is not available")
+    task.start_pos, task.seqlen = 0, 19          # 19 tokens: pages 0, 1 (main) and the first page of the region on
+    d = pack_descriptors([task], [cache])
+    ids = d["kv_page_indices"].tolist()
+    assert ids[:2] == [0, 1] and ids[2] == main and d["kv_last_page_lens"].tolist() == [3]
+    assert pool.rows_used[0] == 3                # the request's last page sits in the region: 3 rows
+    assert pool._rows_of(main, 1, np.array([False, True, True])) == 3
+    assert pool._rows_of(main, 0, np.array([True, True, True])) == 0
+    task.start_pos, task.seqlen = 19, 6          # 25 tokens: the region page is full, a second one holds 1 row
+    d = pack_descriptors([task], [cache])
+    assert d["kv_page_indices"].tolist()[2:] == [main, main + 1]
+    assert pool.rows_used[:2].tolist() == [ps, 1]
+    assert pool._rows_of(main, 2, np.array([False, False, True])) == ps
+    pool.rows_used[0] = 2
+    pool.free(np.array([main]))                  # whoever gets the page next holds a whole page until told otherwise
+    assert pool.rows_used[0] == ps
+    plain = dk.GpuPagePool(1, 4, ps, CPU, torch.float16, n_kv_heads=1, head_dim=8) if hasattr(dk, "GpuPagePool") else None
+    assert plain is None or getattr(plain, "rows_used", None) is None
