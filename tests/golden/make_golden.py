@@ -217,7 +217,7 @@ def main(ref_root: str) -> None:
     out["virtual_traces"] = [virtual_trace(0, 6, 4, 16, 2, 12), virtual_trace(1, 20, 10, 8, 3, 18),
                              virtual_trace(2, 12, 8, 16, 4, 16)]
 
-    # the hand-written scenario of the survey (A.2)
+    # a hand-written scenario: two microbatches alternating over a 6 + 4 + 4 page pool
     pool = VirtualPagePool(1, 6, 4, 16, cpu, torch.float16)
     pta = PageTableAllocator(8, 4096, 16, cpu)
     a2 = [{"op": "init", "state": vstate(pool)}]
