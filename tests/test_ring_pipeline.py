@@ -42,6 +42,7 @@ class _GlooHop:
         self.dist, self.nxt, self.prv = dist, (rank + 1) % world, (rank - 1) % world
         self.sent = self.received = self.released = 0
         self._pending = []
+        self.depth = 16  # inbox buffers: the ring asks for microbatches - stages + 2
 
     def send(self, y):
         self._pending.append(self.dist.isend(torch.cat([torch.tensor([float(self.sent)]), y.flatten()]), self.nxt))
@@ -106,7 +107,8 @@ def _worker(rank, world, port, steps, split, q, mbs=None):
 
 @pytest.mark.parametrize("world,steps,split,mbs", [(2, 3, [2], None), (3, 2, [3, 1], None), (2, 1, [], None),
                                                    (3, 3, "hop", None), (4, 2, "hop", None),
-                                                   (2, 3, [5], 4), (3, 2, [4, 3], 5), (2, 2, [], 8)])
+                                                   (2, 3, [5], 4), (3, 2, [4, 3], 5), (2, 2, [], 8),
+                                                   (2, 3, "hop", 4), (3, 2, "hop", 5)])
 def test_ring_pipeline_matches_sequential(world, steps, split, mbs):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
